@@ -8,7 +8,8 @@ KVSpec form a group that shares page ids and has a pool of its own:
     pool[group]   [layers of the group, pages, 2 (k, v), kv heads, page_size, head_dim]
                   (values of another size than the keys: [layers, pages, kv heads * page_size * (head_dim + v_dim)],
                   a page's keys [kv heads, page_size, head_dim] followed by its values [kv heads, page_size, v_dim];
-                  values inside the keys: [layers, pages, kv heads * page_size * head_dim])
+                  values inside the keys: [layers, pages, kv heads * page_size * head_dim];
+                  v_share key heads to a value head: the values are [kv heads / v_share, page_size, v_dim])
     state[cache]  [max_requests, *shape]     one row per request slot
 
 A request holds one slot from open() to close(); its state rows are zeroed
@@ -29,12 +30,15 @@ class KVSpec:
     """Keys and values of `num_kv_heads` heads of `head_dim`; window = 0 keeps every position; v_dim = 0: values of
     the keys' size, else their own size (a page then holds the keys of its slots followed by the values).
     value_in_key: a key's first v_dim values ARE its value; the cache then holds the keys alone (a latent that is
-    read both as part of the key and as the value is stored once)."""
+    read both as part of the key and as the value is stored once).
+    v_share > 1: that many neighbouring key heads read one value head (several score maps over the same values); a page
+    then holds num_kv_heads heads of keys followed by num_kv_heads / v_share heads of values."""
     num_kv_heads: int
     head_dim: int
     window: int = 0
     v_dim: int = 0
     value_in_key: bool = False
+    v_share: int = 1
 
 
 @dataclass(frozen=True)
@@ -70,6 +74,10 @@ class CacheManager:
                 by_spec.setdefault(spec, []).append(cid)
         self.groups = [PageGroup(tuple(ids), s.num_kv_heads, s.head_dim, s.window) for s, ids in by_spec.items()]
         self._v_dims = [0 if s.value_in_key else (s.v_dim or s.head_dim) for s in by_spec]      # values stored beside the keys
+        self._v_heads = [s.num_kv_heads // max(1, s.v_share) for s in by_spec]
+        for s in by_spec:
+            if s.v_share < 1 or s.num_kv_heads % s.v_share or (s.value_in_key and s.v_share != 1):
+                raise ValueError("key heads do not divide into the value heads they share")
         if isinstance(num_pages, int):
             num_pages = [num_pages] * len(self.groups)
         self.tables = PageTables(self.groups, page_size, list(num_pages), max_requests)
@@ -78,8 +86,10 @@ class CacheManager:
         for g, grp in enumerate(self.groups):
             pool = None
             if allocate:
-                shape = ((2, grp.num_kv_heads, page_size, grp.head_dim) if self._v_dims[g] == grp.head_dim and not list(by_spec)[g].value_in_key
-                         else (grp.num_kv_heads * page_size * (grp.head_dim + self._v_dims[g]),))
+                spec = list(by_spec)[g]
+                shape = ((2, grp.num_kv_heads, page_size, grp.head_dim)
+                         if self._v_dims[g] == grp.head_dim and not spec.value_in_key and spec.v_share == 1
+                         else (page_size * (grp.num_kv_heads * grp.head_dim + self._v_heads[g] * self._v_dims[g]),))
                 pool = torch.zeros((len(grp.cache_ids), self.tables.pools[g].num_pages, *shape), dtype=dtype, device=self.device)
             self.pools.append(pool)
             for i, cid in enumerate(grp.cache_ids):
@@ -93,7 +103,8 @@ class CacheManager:
     def bytes_per_token(self) -> int:
         """Cache bytes one position takes over all groups (every layer, keys and values)."""
         size = torch.empty((), dtype=self.dtype).element_size()
-        return sum(len(g.cache_ids) * g.num_kv_heads * (g.head_dim + vd) * size for g, vd in zip(self.groups, self._v_dims))
+        return sum(len(g.cache_ids) * (g.num_kv_heads * g.head_dim + vh * vd) * size
+                   for g, vd, vh in zip(self.groups, self._v_dims, self._v_heads))
 
     def token_capacity(self) -> int:
         """Positions the smallest pool can hold."""

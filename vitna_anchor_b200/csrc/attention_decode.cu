@@ -46,7 +46,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) attention_decode_kernel(
     const int32_t* __restrict__ token_seg, const int32_t* __restrict__ positions, const int32_t* __restrict__ tok_list,
     T* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ counters, int nh, int nkv,
     int hd, int page_size, int max_blocks, int max_splits, float scale, int window, int vd, const float* __restrict__ dist_bias,
-    int max_dist, int v_in_key) {
+    int max_dist, int v_in_key, int v_share) {
     constexpr int V = Vec16<T>::N;
     extern __shared__ float smem[];
     const int g = nh / nkv;
@@ -81,7 +81,9 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) attention_decode_kernel(
 
     const int32_t* bt = block_tables + (size_t)token_seg[t] * max_blocks;
     // v_in_key: a key's first vd values are its value (a page holds the keys alone)
-    const size_t page_stride = (size_t)nkv * page_size * (v_in_key ? hd : hd + vd);
+    // v_share: that many neighbouring key heads read one value head (a page then holds nkv / v_share heads of values)
+    const size_t page_stride = (size_t)page_size * (v_in_key ? nkv * hd : nkv * hd + nkv / v_share * vd);
+    const int vh = kvh / v_share;
     const size_t v_base = v_in_key ? 0 : (size_t)nkv * page_size * hd;        // where a page's values begin
     const int v_stride = v_in_key ? hd : vd;
     const int key = k0 + tid;
@@ -102,7 +104,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) attention_decode_kernel(
                 const T* pg = cache + (size_t)bt[kk / page_size] * page_stride;
                 const size_t in_page = (size_t)kvh * page_size + kk % page_size;
                 if (part < chk) dec_cp_async16(sk + kl * lds + part * V, pg + in_page * hd + part * V);
-                else dec_cp_async16(sv + kl * ldv + (part - chk) * V, pg + v_base + in_page * v_stride + (part - chk) * V);
+                else dec_cp_async16(sv + kl * ldv + (part - chk) * V, pg + v_base + ((size_t)vh * page_size + kk % page_size) * v_stride + (part - chk) * V);
             }
         }
     }
@@ -190,7 +192,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) attention_decode_kernel(
                 if (row < nkeys && row >= row_lo) {
                     const int kk = k0 + row;
                     const T* vr = ASYNC ? sv + row * ldv
-                                        : cache + (size_t)bt[kk / page_size] * page_stride + v_base + ((size_t)kvh * page_size + kk % page_size) * v_stride;
+                                        : cache + (size_t)bt[kk / page_size] * page_stride + v_base + ((size_t)vh * page_size + kk % page_size) * v_stride;
                     load16<T>(vr + c, vf[i]);
                 } else {
 #pragma unroll
@@ -382,7 +384,7 @@ VK_API int vk_attention_decode(const void* q, const void* cache, const int32_t* 
         }                                                                                                                            \
         return launch_dependent(kern, grid, dim3(DEC_THREADS), smem, stream, (const T*)q, (const T*)cache, block_tables, token_seg, \
                                 positions, tok_list, (T*)out, part_o, part_ml, counters, nh, nkv, hd, page_size, max_blocks, splits, \
-                                scale, window, hd, (const float*)nullptr, 0, 0);                                                     \
+                                scale, window, hd, (const float*)nullptr, 0, 0, 1);                                                  \
     }
     if (dtype == 0) {
         if (async) GO(float, true) else GO(float, false)
@@ -396,18 +398,20 @@ VK_API int vk_attention_decode(const void* q, const void* cache, const int32_t* 
 // The same for the unrotated form of the attention: values of size vd (the scratch is
 // vk_attention_decode_scratch_bytes(tokens, nh, nkv, max(hd, vd), max_context) bytes) and an optional bias by distance.
 // v_in_key: the cache holds keys alone and a key's first vd values are its value (vd <= hd).
+// v_share > 1: key heads v_share*j .. v_share*j + v_share-1 read value head j (a page holds nkv / v_share heads of values).
 // Always the CUDA-core kernel, in both dtypes.
 VK_API int vk_attention_decode_biased(const void* q, const void* cache, const int32_t* block_tables, const int32_t* token_seg,
                                       const int32_t* positions, const int32_t* tok_list, void* out, void* scratch, int scratch_tokens,
                                       int n_tokens, int nh, int nkv, int hd, int vd, int page_size, int max_blocks, int max_context,
                                       int grid_context, float scale, int window, const float* dist_bias, int max_dist, int v_in_key,
-                                      int dtype, cudaStream_t stream) {
+                                      int v_share, int dtype, cudaStream_t stream) {
     if (n_tokens <= 0) return VK_OK;
     if (nh <= 0 || nkv <= 0 || nh % nkv != 0 || hd <= 0 || vd <= 0 || page_size <= 0 || max_blocks <= 0 || window < 0 || max_context <= 0 ||
         grid_context <= 0 || grid_context > max_context || (dist_bias && max_dist <= 0))
         return VK_BAD_SHAPE;
     const int vec = dtype == 0 ? 4 : 8;
     if (hd % vec != 0 || vd % vec != 0 || (v_in_key && vd > hd)) return VK_BAD_SHAPE;
+    if (v_share < 1 || nkv % v_share != 0 || (v_in_key && v_share != 1)) return VK_BAD_SHAPE;
     if (hd > DEC_MAX_HD || vd > DEC_MAX_HD || vd / vec > 32 || n_tokens > scratch_tokens || n_tokens > 65535 || max_context > 128 * DEC_SPLIT)
         return VK_TOO_LARGE;
     if (((uintptr_t)cache % 16) || ((uintptr_t)scratch % 16) || ((uintptr_t)q % 4)) return VK_BAD_ALIGNMENT;
@@ -434,7 +438,7 @@ VK_API int vk_attention_decode_biased(const void* q, const void* cache, const in
         }                                                                                                                            \
         return launch_dependent(kern, grid, dim3(DEC_THREADS), smem, stream, (const T*)q, (const T*)cache, block_tables, token_seg, \
                                 positions, tok_list, (T*)out, part_o, part_ml, counters, nh, nkv, hd, page_size, max_blocks, splits, \
-                                scale, window, vd, dist_bias, max_dist, v_in_key);                                                   \
+                                scale, window, vd, dist_bias, max_dist, v_in_key, v_share);                                          \
     }
     if (dtype == 0) {
         if (async) GO(float, true) else GO(float, false)
@@ -513,7 +517,7 @@ VK_API int vk_attention_decode_static(const void* q, const void* cache, const in
         }                                                                                                                     \
         kern<<<grid, DEC_THREADS, smem, stream>>>((const T*)q, (const T*)cache, block_tables, token_seg, positions, tok_list, \
                                                   (T*)out, part_o, part_ml, counters, nh, nkv, hd, page_size, max_blocks,     \
-                                                  splits, scale, window, hd, (const float*)nullptr, 0, 0);                    \
+                                                  splits, scale, window, hd, (const float*)nullptr, 0, 0, 1);                 \
     }
     if (dtype == 0) {
         if (async) GO(float, true) else GO(float, false)

@@ -60,7 +60,7 @@ template <int HD, int VD>
 __global__ void __launch_bounds__(PF_THREADS, 2) attention_prefill_kernel(
     const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ cache, const int32_t* __restrict__ block_tables,
     const int32_t* __restrict__ tiles, __nv_bfloat16* __restrict__ out, int nh, int nkv, int page_size, int max_blocks, float scale,
-    int window, const float* __restrict__ dist_bias, int max_dist, int v_in_key) {
+    int window, const float* __restrict__ dist_bias, int max_dist, int v_in_key, int v_share) {
     typedef __nv_bfloat16 T;
     constexpr int LD = HD + 8;                      // padded row: 16-byte shifts keep ldmatrix free of bank conflicts
     constexpr int LDV = VD + 8;
@@ -81,7 +81,9 @@ __global__ void __launch_bounds__(PF_THREADS, 2) attention_prefill_kernel(
     const int g = lane >> 2, qd = lane & 3;
     const int32_t* bt = block_tables + (size_t)seg * max_blocks;
     // v_in_key: a key's first VD values are its value (a page holds the keys alone)
-    const size_t page_stride = (size_t)nkv * page_size * (v_in_key ? HD : HD + VD);
+    // v_share: that many neighbouring key heads read one value head (a page then holds nkv / v_share heads of values)
+    const size_t page_stride = (size_t)page_size * (v_in_key ? nkv * HD : nkv * HD + nkv / v_share * VD);
+    const int vh = kvh / v_share;
     const size_t v_base = v_in_key ? 0 : (size_t)nkv * page_size * HD;       // where a page's values begin
     const int v_stride = v_in_key ? HD : VD;
 
@@ -113,7 +115,8 @@ __global__ void __launch_bounds__(PF_THREADS, 2) attention_prefill_kernel(
             if (key <= last_pos && key >= lo_first) {
                 const T* pg = cache + (size_t)bt[key / page_size] * page_stride;
                 const size_t in_page = (size_t)kvh * page_size + key % page_size;
-                cp_async16(dst, c < CHUNKS ? pg + in_page * HD + c * 8 : pg + v_base + in_page * v_stride + (c - CHUNKS) * 8);
+                cp_async16(dst, c < CHUNKS ? pg + in_page * HD + c * 8
+                                            : pg + v_base + ((size_t)vh * page_size + key % page_size) * v_stride + (c - CHUNKS) * 8);
             } else {                                // never read as a key (masked), but keep the values finite
                 *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
             }
@@ -323,7 +326,7 @@ __global__ void __launch_bounds__(PF_THREADS, 2) attention_prefill_kernel(
 template <int HD, int VD>
 static int launch_prefill(const void* q, const void* cache, const int32_t* bt, const int32_t* tiles, void* out, int n_tiles, int nh,
                           int nkv, int page_size, int max_blocks, float scale, int window, const float* dist_bias, int max_dist,
-                          int v_in_key, cudaStream_t stream) {
+                          int v_in_key, int v_share, cudaStream_t stream) {
     constexpr int LD = HD + 8, LDV = VD + 8;
     size_t smem = (size_t)(PF_BM * LD + 4 * PF_BN * (LD + LDV)) * 2 + 4 * 128 * sizeof(float);
     const size_t hand = (size_t)(PF_BM * LD + 2 * PF_BN * (LD + LDV)) * 2 + (size_t)PF_GROUP * (VD / 8 * 4 + 4) * sizeof(float);
@@ -335,14 +338,14 @@ static int launch_prefill(const void* q, const void* cache, const int32_t* bt, c
     }
     dim3 grid(n_tiles, nh);
     return launch_plain(kern, grid, dim3(PF_THREADS), smem, stream, (const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, bt, tiles,
-                            (__nv_bfloat16*)out, nh, nkv, page_size, max_blocks, scale, window, dist_bias, max_dist, v_in_key);
+                            (__nv_bfloat16*)out, nh, nkv, page_size, max_blocks, scale, window, dist_bias, max_dist, v_in_key, v_share);
 }
 
 template <int HD>
 static int launch_prefill_v(int vd, const void* q, const void* cache, const int32_t* bt, const int32_t* tiles, void* out, int n_tiles, int nh,
                             int nkv, int page_size, int max_blocks, float scale, int window, const float* dist_bias, int max_dist,
-                            int v_in_key, cudaStream_t stream) {
-#define GO(VD) return launch_prefill<HD, VD>(q, cache, bt, tiles, out, n_tiles, nh, nkv, page_size, max_blocks, scale, window, dist_bias, max_dist, v_in_key, stream)
+                            int v_in_key, int v_share, cudaStream_t stream) {
+#define GO(VD) return launch_prefill<HD, VD>(q, cache, bt, tiles, out, n_tiles, nh, nkv, page_size, max_blocks, scale, window, dist_bias, max_dist, v_in_key, v_share, stream)
     switch (vd) {
         case 32: GO(32);
         case 64: GO(64);
@@ -366,7 +369,7 @@ VK_API int vk_attention_prefill(const void* q, const void* cache, const int32_t*
     if (nh <= 0 || nkv <= 0 || nh % nkv != 0 || page_size <= 0 || max_blocks <= 0 || window < 0) return VK_BAD_SHAPE;
     if (nh > 65535) return VK_TOO_LARGE;
     if (((uintptr_t)q % 16) || ((uintptr_t)cache % 16) || ((uintptr_t)out % 4)) return VK_BAD_ALIGNMENT;
-#define GO(HD) return launch_prefill<HD, HD>(q, cache, block_tables, tiles, out, n_tiles, nh, nkv, page_size, max_blocks, scale, window, nullptr, 0, 0, stream)
+#define GO(HD) return launch_prefill<HD, HD>(q, cache, block_tables, tiles, out, n_tiles, nh, nkv, page_size, max_blocks, scale, window, nullptr, 0, 0, 1, stream)
     switch (hd) {
         case 16: GO(16);
         case 32: GO(32);
@@ -381,15 +384,17 @@ VK_API int vk_attention_prefill(const void* q, const void* cache, const int32_t*
 // The same for the unrotated form of the attention: values of size vd (out [all tokens, nh*vd]; a page holds its keys, then
 // its values) and an optional bias by distance.  Head sizes 32, 64, 96 and 128 for keys and for values, in any pairing.
 // v_in_key: the cache holds keys alone and a key's first vd values are its value (vd <= hd).
+// v_share > 1: key heads v_share*j .. v_share*j + v_share-1 read value head j (a page holds nkv / v_share heads of values).
 VK_API int vk_attention_prefill_biased(const void* q, const void* cache, const int32_t* block_tables, const int32_t* tiles, void* out,
                                        int n_tiles, int nh, int nkv, int hd, int vd, int page_size, int max_blocks, float scale, int window,
-                                       const float* dist_bias, int max_dist, int v_in_key, cudaStream_t stream) {
+                                       const float* dist_bias, int max_dist, int v_in_key, int v_share, cudaStream_t stream) {
     if (n_tiles <= 0) return VK_OK;
     if (nh <= 0 || nkv <= 0 || nh % nkv != 0 || page_size <= 0 || max_blocks <= 0 || window < 0 || (dist_bias && max_dist <= 0)) return VK_BAD_SHAPE;
     if (v_in_key && vd > hd) return VK_BAD_SHAPE;
+    if (v_share < 1 || nkv % v_share != 0 || (v_in_key && v_share != 1)) return VK_BAD_SHAPE;
     if (nh > 65535) return VK_TOO_LARGE;
     if (((uintptr_t)q % 16) || ((uintptr_t)cache % 16) || ((uintptr_t)out % 4)) return VK_BAD_ALIGNMENT;
-#define GO(HD) return launch_prefill_v<HD>(vd, q, cache, block_tables, tiles, out, n_tiles, nh, nkv, page_size, max_blocks, scale, window, dist_bias, max_dist, v_in_key, stream)
+#define GO(HD) return launch_prefill_v<HD>(vd, q, cache, block_tables, tiles, out, n_tiles, nh, nkv, page_size, max_blocks, scale, window, dist_bias, max_dist, v_in_key, v_share, stream)
     switch (hd) {
         case 32: GO(32);
         case 64: GO(64);

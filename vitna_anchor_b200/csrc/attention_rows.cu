@@ -31,7 +31,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_rows_kernel(
     const T* __restrict__ q, const T* __restrict__ cache, const int32_t* __restrict__ block_tables,
     const int32_t* __restrict__ token_seg, const int32_t* __restrict__ positions, const int32_t* __restrict__ tok_list,
     T* __restrict__ out, int nh, int nkv, int hd, int vd, int page_size, int max_blocks, float scale, int window,
-    const float* __restrict__ dist_bias, int max_dist, int v_in_key) {
+    const float* __restrict__ dist_bias, int max_dist, int v_in_key, int v_share) {
     extern __shared__ float smem[];
     float* qs = smem;                         // [hd]
     float* pr = qs + hd;                      // [128]
@@ -44,7 +44,8 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_rows_kernel(
     const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
     const int32_t* bt = block_tables + (size_t)token_seg[t] * max_blocks;
     // v_in_key: a key's first vd values are its value (a page holds the keys alone)
-    const size_t page_stride = (size_t)nkv * page_size * (v_in_key ? hd : hd + vd);
+    // v_share: that many neighbouring key heads read one value head (a page then holds nkv / v_share heads of values)
+    const size_t page_stride = (size_t)page_size * (v_in_key ? nkv * hd : nkv * hd + nkv / v_share * vd);
     const size_t v_base = v_in_key ? 0 : (size_t)nkv * page_size * hd;     // where a page's values begin
     const int v_stride = v_in_key ? hd : vd;
 
@@ -62,7 +63,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_rows_kernel(
         if (valid) {
             const int page = bt[key / page_size];
             const size_t in_page = (size_t)kvh * page_size + key % page_size;
-            row_off[tid] = (size_t)page * page_stride + v_base + in_page * v_stride;      // the key's row of values
+            row_off[tid] = (size_t)page * page_stride + v_base + ((size_t)(kvh / v_share) * page_size + key % page_size) * v_stride;   // the key's row of values
             const T* kr = cache + (size_t)page * page_stride + in_page * hd;
             float dot = 0.0f;
             for (int d = 0; d < hd; d++) dot = fmaf(qs[d], to_f32<T>(kr[d]), dot);
@@ -108,16 +109,18 @@ using namespace vk;
 
 // q [tokens, nh*hd], out [tokens, nh*vd]; cache: one layer [pages][ nkv*page_size*hd keys | nkv*page_size*vd values ];
 // block_tables [segments, max_blocks]; token_seg, positions [all tokens]; tok_list [tokens] names the
-// tokens to run (null: 0..tokens-1); dist_bias [max_dist][nh] float32 or null.  v_in_key: the cache holds keys alone,
+// tokens to run (null: 0..tokens-1); dist_bias [max_dist][nh] float32 or null.  v_share > 1: key heads v_share*j .. v_share*j + v_share-1 read value
+// head j, and a page holds [nkv][page_size][hd] keys followed by [nkv / v_share][page_size][vd] values.  v_in_key: the cache holds keys alone,
 // [pages][nkv*page_size*hd], and a key's first vd values are its value (vd <= hd).
 VK_API int vk_attention_rows_biased(const void* q, const void* cache, const int32_t* block_tables, const int32_t* token_seg,
                                     const int32_t* positions, const int32_t* tok_list, void* out, int tokens, int nh, int nkv, int hd, int vd,
                                     int page_size, int max_blocks, float scale, int window, const float* dist_bias, int max_dist, int v_in_key,
-                                    int dtype, cudaStream_t stream) {
+                                    int v_share, int dtype, cudaStream_t stream) {
     if (tokens <= 0) return VK_OK;
     if (nh <= 0 || nkv <= 0 || nh % nkv != 0 || hd <= 0 || vd <= 0 || page_size <= 0 || max_blocks <= 0 || window < 0) return VK_BAD_SHAPE;
     if (dist_bias && max_dist <= 0) return VK_BAD_SHAPE;
     if (v_in_key && vd > hd) return VK_BAD_SHAPE;
+    if (v_share < 1 || nkv % v_share != 0 || (v_in_key && v_share != 1)) return VK_BAD_SHAPE;
     if (vd > ATT_THREADS * ATT_MAX_ACC || nh > 65535) return VK_TOO_LARGE;
     const size_t smem = (size_t)(hd + ATT_THREADS + 32) * sizeof(float);
     if (smem > 48 * 1024) return VK_TOO_LARGE;
@@ -125,11 +128,11 @@ VK_API int vk_attention_rows_biased(const void* q, const void* cache, const int3
     if (dtype == 0)
         attention_rows_kernel<float><<<grid, ATT_THREADS, smem, stream>>>((const float*)q, (const float*)cache, block_tables,
                                                                           token_seg, positions, tok_list, (float*)out, nh, nkv, hd, vd,
-                                                                          page_size, max_blocks, scale, window, dist_bias, max_dist, v_in_key);
+                                                                          page_size, max_blocks, scale, window, dist_bias, max_dist, v_in_key, v_share);
     else
         attention_rows_kernel<__nv_bfloat16><<<grid, ATT_THREADS, smem, stream>>>(
             (const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, block_tables, token_seg, positions, tok_list, (__nv_bfloat16*)out, nh,
-            nkv, hd, vd, page_size, max_blocks, scale, window, dist_bias, max_dist, v_in_key);
+            nkv, hd, vd, page_size, max_blocks, scale, window, dist_bias, max_dist, v_in_key, v_share);
     return launch_status();
 }
 
@@ -139,5 +142,5 @@ VK_API int vk_attention_rows(const void* q, const void* cache, const int32_t* bl
                              int max_blocks, float scale, int window, int dtype, cudaStream_t stream) {
     if (hd > ATT_THREADS * ATT_MAX_ACC) return VK_TOO_LARGE;
     return vk_attention_rows_biased(q, cache, block_tables, token_seg, positions, tok_list, out, tokens, nh, nkv, hd, hd, page_size, max_blocks,
-                                    scale, window, nullptr, 0, 0, dtype, stream);
+                                    scale, window, nullptr, 0, 0, 1, dtype, stream);
 }

@@ -752,16 +752,18 @@ def hyper_step(xs: torch.Tensor, y: Optional[torch.Tensor], streams: int, *, mix
 # Attention without a rotation: unit-RMS q and k, a query factor that grows with the position, a bias by distance
 # ---------------------------------------------------------------------------
 
-def kv_page_elems(nkv: int, page_size: int, hd: int, vd: int) -> int:
-    """Elements of one page of one layer: [nkv][page_size][hd] keys, then [nkv][page_size][vd] values."""
-    return nkv * page_size * (hd + vd)
+def kv_page_elems(nkv: int, page_size: int, hd: int, vd: int, v_share: int = 1) -> int:
+    """Elements of one page of one layer: [nkv][page_size][hd] keys, then [nkv / v_share][page_size][vd] values
+    (v_share neighbouring key heads read one value head)."""
+    return page_size * (nkv * hd + nkv // v_share * vd)
 
 
-def _page_size_of(cache_layer: torch.Tensor, nkv: int, hd: int, vd: int) -> int:
+def _page_size_of(cache_layer: torch.Tensor, nkv: int, hd: int, vd: int, v_share: int = 1) -> int:
     per_page = cache_layer[0].numel()
-    ps = per_page // (nkv * (hd + vd))
-    if ps < 1 or ps * nkv * (hd + vd) != per_page or not cache_layer.is_contiguous():
-        raise KernelError("the cache layer is not [pages][nkv * page_size * (hd + vd)]")
+    one = nkv * hd + nkv // v_share * vd
+    ps = per_page // one
+    if ps < 1 or ps * one != per_page or nkv % v_share or not cache_layer.is_contiguous():
+        raise KernelError("the cache layer is not [pages][page_size * (nkv * hd + nkv / v_share * vd)]")
     return ps
 
 
@@ -787,14 +789,15 @@ def qk_norm_store(qkv: torch.Tensor, positions: torch.Tensor, slot_mapping: Opti
 def attention_rows_biased(q: torch.Tensor, cache_layer: torch.Tensor, block_tables: torch.Tensor, token_seg: torch.Tensor,
                           positions: torch.Tensor, out: torch.Tensor, nh: int, nkv: int, hd: int, vd: int, page_size: int, scale: float,
                           window: int = 0, dist_bias: Optional[torch.Tensor] = None, tok_list: Optional[torch.Tensor] = None,
-                          v_in_key: bool = False) -> torch.Tensor:
+                          v_in_key: bool = False, v_share: int = 1) -> torch.Tensor:
     """Causal attention of every token (or of those in tok_list) over its request's pages, any sizes, float32 arithmetic,
     with values of size vd and, if given, dist_bias [distances, nh] (float32) added to the scaled scores by min(distance, last row).
-    v_in_key: the cache holds keys alone and a key's first vd values are its value."""
+    v_in_key: the cache holds keys alone and a key's first vd values are its value.  v_share > 1: that many neighbouring
+    key heads read one value head (two score maps over the same values)."""
     _req(q, "q", dims=2); _req(cache_layer, "cache_layer", q.dtype); _req(block_tables, "block_tables", torch.int32, 2)
     _req(token_seg, "token_seg", torch.int32, 1); _req(positions, "positions", torch.int32, 1); _req(out, "out", q.dtype, 2)
     T = q.shape[0]
-    if q.shape[1] != nh * hd or out.shape != (T, nh * vd) or _page_size_of(cache_layer, nkv, hd, 0 if v_in_key else vd) != page_size:
+    if q.shape[1] != nh * hd or out.shape != (T, nh * vd) or _page_size_of(cache_layer, nkv, hd, 0 if v_in_key else vd, v_share) != page_size:
         raise KernelError("attention_rows_biased: shapes do not fit the head counts")
     if token_seg.shape[0] != T or positions.shape[0] != T:
         raise KernelError("attention_rows_biased: per-token arrays differ in length")
@@ -808,7 +811,7 @@ def attention_rows_biased(q: torch.Tensor, cache_layer: torch.Tensor, block_tabl
         n = tok_list.shape[0]
     _check(lib().vk_attention_rows_biased(_p(q), _p(cache_layer), _p(block_tables), _p(token_seg), _p(positions), _p(tok_list), _p(out), n, nh,
                                           nkv, hd, vd, page_size, block_tables.shape[1], ctypes.c_float(scale), window, _p(dist_bias),
-                                          0 if dist_bias is None else dist_bias.shape[0], int(v_in_key), _dt(q), _stream()),
+                                          0 if dist_bias is None else dist_bias.shape[0], int(v_in_key), int(v_share), _dt(q), _stream()),
            "attention_rows_biased")
     return out
 
@@ -892,14 +895,14 @@ def attention_decode_biased(q: torch.Tensor, cache_layer: torch.Tensor, block_ta
                             positions: torch.Tensor, out: torch.Tensor, scratch: torch.Tensor, scratch_tokens: int, nh: int, nkv: int, hd: int,
                             vd: int, page_size: int, scale: float, max_context: int, grid_context: int, window: int = 0,
                             dist_bias: Optional[torch.Tensor] = None, tok_list: Optional[torch.Tensor] = None,
-                            v_in_key: bool = False) -> torch.Tensor:
+                            v_in_key: bool = False, v_share: int = 1) -> torch.Tensor:
     """The split-key attention of single decoded tokens in the unrotated form: values of size vd, an optional bias by distance.
     scratch: attention_decode_scratch_bytes(scratch_tokens, nh, nkv, max(hd, vd), max_context) bytes, zero at first use."""
     _req(q, "q", dims=2); _req(cache_layer, "cache_layer", q.dtype); _req(block_tables, "block_tables", torch.int32, 2)
     _req(token_seg, "token_seg", torch.int32, 1); _req(positions, "positions", torch.int32, 1); _req(out, "out", q.dtype, 2)
     _req(scratch, "scratch", torch.uint8, 1)
     T = q.shape[0]
-    if q.shape[1] != nh * hd or out.shape != (T, nh * vd) or _page_size_of(cache_layer, nkv, hd, 0 if v_in_key else vd) != page_size:
+    if q.shape[1] != nh * hd or out.shape != (T, nh * vd) or _page_size_of(cache_layer, nkv, hd, 0 if v_in_key else vd, v_share) != page_size:
         raise KernelError("attention_decode_biased: shapes do not fit the head counts")
     if dist_bias is not None:
         _req(dist_bias, "dist_bias", torch.float32, 2)
@@ -914,7 +917,7 @@ def attention_decode_biased(q: torch.Tensor, cache_layer: torch.Tensor, block_ta
     _check(lib().vk_attention_decode_biased(_p(q), _p(cache_layer), _p(block_tables), _p(token_seg), _p(positions), _p(tok_list), _p(out),
                                             _p(scratch), scratch_tokens, n, nh, nkv, hd, vd, page_size, block_tables.shape[1], max_context,
                                             grid_context, ctypes.c_float(scale), window, _p(dist_bias),
-                                            0 if dist_bias is None else dist_bias.shape[0], int(v_in_key), _dt(q), _stream()),
+                                            0 if dist_bias is None else dist_bias.shape[0], int(v_in_key), int(v_share), _dt(q), _stream()),
            "attention_decode_biased")
     return out
 
@@ -924,12 +927,12 @@ BIASED_PREFILL_HEAD_SIZES = (32, 64, 96, 128)
 
 def attention_prefill_biased(q: torch.Tensor, cache_layer: torch.Tensor, block_tables: torch.Tensor, tiles: torch.Tensor, out: torch.Tensor,
                              nh: int, nkv: int, hd: int, vd: int, page_size: int, scale: float, window: int = 0,
-                             dist_bias: Optional[torch.Tensor] = None, v_in_key: bool = False) -> torch.Tensor:
+                             dist_bias: Optional[torch.Tensor] = None, v_in_key: bool = False, v_share: int = 1) -> torch.Tensor:
     """Causal attention of prompt portions in bfloat16 on the tensor cores, in the unrotated form.  tiles int32 [n, 4]: first
     token, rows (1..64), position of the first token, segment."""
     _req(q, "q", torch.bfloat16, 2); _req(cache_layer, "cache_layer", torch.bfloat16)
     _req(block_tables, "block_tables", torch.int32, 2); _req(tiles, "tiles", torch.int32, 2); _req(out, "out", torch.bfloat16, 2)
-    if (q.shape[1] != nh * hd or out.shape != (q.shape[0], nh * vd) or _page_size_of(cache_layer, nkv, hd, 0 if v_in_key else vd) != page_size
+    if (q.shape[1] != nh * hd or out.shape != (q.shape[0], nh * vd) or _page_size_of(cache_layer, nkv, hd, 0 if v_in_key else vd, v_share) != page_size
             or tiles.shape[1] != 4):
         raise KernelError("attention_prefill_biased: shapes do not fit the head counts")
     if hd not in BIASED_PREFILL_HEAD_SIZES or vd not in BIASED_PREFILL_HEAD_SIZES:
@@ -940,15 +943,15 @@ def attention_prefill_biased(q: torch.Tensor, cache_layer: torch.Tensor, block_t
             raise KernelError("attention_prefill_biased: the bias table is not [distances, heads]")
     _check(lib().vk_attention_prefill_biased(_p(q), _p(cache_layer), _p(block_tables), _p(tiles), _p(out), tiles.shape[0], nh, nkv, hd, vd,
                                              page_size, block_tables.shape[1], ctypes.c_float(scale), window, _p(dist_bias),
-                                             0 if dist_bias is None else dist_bias.shape[0], int(v_in_key), _stream()), "attention_prefill_biased")
+                                             0 if dist_bias is None else dist_bias.shape[0], int(v_in_key), int(v_share), _stream()), "attention_prefill_biased")
     return out
 
 
 def attention_biased(q: torch.Tensor, pages: torch.Tensor, meta, ctx, out: torch.Tensor, nh: int, nkv: int, hd: int, vd: int,
                      page_size: int, scale: float, window: int = 0, dist_bias: Optional[torch.Tensor] = None,
-                     v_in_key: bool = False) -> torch.Tensor:
+                     v_in_key: bool = False, v_share: int = 1) -> torch.Tensor:
     """Causal attention of a mixed batch over the paged cache in the unrotated form (values of their own size, or the
-    first vd values of the keys with v_in_key; a bias by distance); `meta` is the page group's GroupMeta.  Single decoded tokens take the split-key kernel, tokens of prompt
+    first vd values of the keys with v_in_key; v_share neighbouring key heads reading one value head; a bias by distance); `meta` is the page group's GroupMeta.  Single decoded tokens take the split-key kernel, tokens of prompt
     portions the tensor-core kernel (bfloat16, head sizes it is built for); whatever is left, and the whole exact 32-bit
     routing, takes attention_rows_biased, which takes every size."""
     vec = 4 if q.dtype == torch.float32 else 8
@@ -958,16 +961,16 @@ def attention_biased(q: torch.Tensor, pages: torch.Tensor, meta, ctx, out: torch
     pre_ok = (bool(ctx.num_pre) and q.dtype == torch.bfloat16 and hd in BIASED_PREFILL_HEAD_SIZES and vd in BIASED_PREFILL_HEAD_SIZES
               and ctx.pre_tiles is not None and q.data_ptr() % 16 == 0 and pages.data_ptr() % 16 == 0)
     rows = lambda toks: attention_rows_biased(q, pages, meta.block_tables, ctx.token_seg, ctx.positions, out, nh, nkv, hd, vd, page_size,
-                                              scale, window, dist_bias, toks, v_in_key)
+                                              scale, window, dist_bias, toks, v_in_key, v_share)
     if dec_ok:
         ws = ctx.workspace
         cap, layout = ws.max_segments, ws.max_context
         nbytes = attention_decode_scratch_bytes(cap, nh, nkv, max(hd, vd), layout)
         scratch = ws.flat(f"att.decb/{nh}/{nkv}/{hd}/{vd}/{layout}", nbytes, torch.uint8, zero=True)
         attention_decode_biased(q, pages, meta.block_tables, ctx.token_seg, ctx.positions, out, scratch, cap, nh, nkv, hd, vd, page_size,
-                                scale, layout, min(layout, max(1, ctx.max_context)), window, dist_bias, ctx.dec_tokens, v_in_key)
+                                scale, layout, min(layout, max(1, ctx.max_context)), window, dist_bias, ctx.dec_tokens, v_in_key, v_share)
     if pre_ok:
-        attention_prefill_biased(q, pages, meta.block_tables, ctx.pre_tiles, out, nh, nkv, hd, vd, page_size, scale, window, dist_bias, v_in_key)
+        attention_prefill_biased(q, pages, meta.block_tables, ctx.pre_tiles, out, nh, nkv, hd, vd, page_size, scale, window, dist_bias, v_in_key, v_share)
     if not dec_ok and not pre_ok:
         return rows(None)
     if ctx.num_pre and not pre_ok:
