@@ -66,3 +66,7 @@ def _register_builtin() -> None:
     from . import siparax as _sxc
     register_architecture(Architecture(_sxc.ARCHITECTURE, _sxc.SiparaxConfig.from_dict, _sx.siparax_manifest, _sx.build_siparax,
                                        _sx.is_norm_weight), replace=True)
+    from ..models import manatar as _mt
+    from . import manatar as _mtc
+    register_architecture(Architecture(_mtc.ARCHITECTURE, _mtc.ManatarConfig.from_dict, _mt.manatar_manifest, _mt.build_manatar,
+                                       _mt.is_norm_weight), replace=True)

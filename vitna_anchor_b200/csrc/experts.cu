@@ -1,0 +1,168 @@
+// A routed feed-forward: every token uses `top` of E small gated feed-forward layers, weighted by a softmax over the chosen logits.
+//
+//  experts_route     one block a token: logits z = W_r x + b in float32 (a warp a logit), the `top` largest (of equal logits the lower
+//                    index), weights = softmax over the chosen logits alone.  Writes ids [tokens][top] and weights [tokens][top].
+//  experts_gate_up   act[token, k] = f(W_gate,e x) * (W_up,e x) for the token's k-th expert e; a warp an output column, the token's row
+//                    in shared memory.  f is one of the epilogues' activations.
+//  experts_down      y[token] += sum_k weight_k W_down,e_k act[token, k], the experts of a token summed in the order of its list, so
+//                    that the sum does not depend on what else is in the batch.
+//
+// Nothing here comes to the host: which experts run is read by the kernels from the ids on the device, so a captured graph
+// replays the part for any batch.  Products accumulate in float32 (fmaf); storage is float32 or bfloat16.
+#include "common.cuh"
+
+namespace vk {
+
+template <typename T>
+__global__ void __launch_bounds__(128) experts_route_kernel(const T* __restrict__ x, int width, const float* __restrict__ wr,
+                                                            const float* __restrict__ br, int E, int top, int32_t* __restrict__ ids,
+                                                            float* __restrict__ wts) {
+    extern __shared__ float z[];                        // [E]
+    dependency_wait();
+    let_dependents_start();
+    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    const T* row = x + (size_t)t * width;
+    for (int e = warp; e < E; e += nwarps) {
+        const float* w = wr + (size_t)e * width;
+        float acc = 0.0f;
+        for (int i = lane; i < width; i += 32) acc = fmaf(to_f32<T>(row[i]), w[i], acc);
+        acc = warp_sum(acc);
+        if (lane == 0) z[e] = acc + (br ? br[e] : 0.0f);
+    }
+    __syncthreads();
+    if (warp != 0) return;
+    // the warp picks the largest logit `top` times; every lane knows each pick, lane k keeps the k-th weight
+    __shared__ int picked[32];
+    float zmax = 0.0f, sum = 0.0f, mine = 0.0f;
+    for (int k = 0; k < top; k++) {
+        float best = -INFINITY;
+        int arg = 0x7fffffff;
+        for (int e = lane; e < E; e += 32) {
+            const float v = z[e];
+            if (v > best || (v == best && e < arg)) {
+                bool taken = false;
+                for (int j = 0; j < k; j++) taken |= picked[j] == e;
+                if (!taken) { best = v; arg = e; }
+            }
+        }
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+            if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
+        }
+        if (arg == 0x7fffffff) arg = 0;                 // logits that are not numbers: stay inside the tables
+        if (k == 0) zmax = best;
+        const float p = expf(best - zmax);
+        sum += p;
+        if (lane == k) mine = p;
+        if (lane == 0) picked[k] = arg;
+        __syncwarp();
+    }
+    if (lane < top) {
+        ids[(size_t)t * top + lane] = picked[lane];
+        wts[(size_t)t * top + lane] = mine / sum;
+    }
+}
+
+// grid (pairs, column groups); a warp a column
+template <typename T>
+__global__ void __launch_bounds__(256) experts_gate_up_kernel(const T* __restrict__ x, int width, const T* __restrict__ wgu, int ff, int top,
+                                                              const int32_t* __restrict__ ids, int act, T* __restrict__ out) {
+    extern __shared__ float xs[];                       // [width]
+    dependency_wait();
+    let_dependents_start();
+    const int p = blockIdx.x, t = p / top;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) xs[i] = to_f32<T>(x[(size_t)t * width + i]);
+    __syncthreads();
+    const int e = ids[p];
+    const T* wg = wgu + (size_t)e * 2 * ff * width;
+    const T* wu = wg + (size_t)ff * width;
+    for (int c = blockIdx.y * nwarps + warp; c < ff; c += gridDim.y * nwarps) {
+        const T* g = wg + (size_t)c * width;
+        const T* u = wu + (size_t)c * width;
+        float ag = 0.0f, au = 0.0f;
+        for (int i = lane; i < width; i += 32) {
+            ag = fmaf(xs[i], to_f32<T>(g[i]), ag);
+            au = fmaf(xs[i], to_f32<T>(u[i]), au);
+        }
+        ag = warp_sum(ag);
+        au = warp_sum(au);
+        if (lane == 0) out[(size_t)p * ff + c] = from_f32<T>(activate_rt(act, ag) * au);
+    }
+}
+
+// grid (tokens, column groups); a warp a column of y
+template <typename T>
+__global__ void __launch_bounds__(256) experts_down_kernel(const T* __restrict__ act, int ff, const T* __restrict__ wd, int width, int top,
+                                                           const int32_t* __restrict__ ids, const float* __restrict__ wts, float* __restrict__ y) {
+    extern __shared__ float as[];                       // [top][ff]
+    dependency_wait();
+    let_dependents_start();
+    const int t = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    for (int i = threadIdx.x; i < top * ff; i += blockDim.x) as[i] = to_f32<T>(act[(size_t)t * top * ff + i]);
+    __syncthreads();
+    for (int c = blockIdx.y * nwarps + warp; c < width; c += gridDim.y * nwarps) {
+        float total = 0.0f;
+        for (int k = 0; k < top; k++) {
+            const int e = ids[(size_t)t * top + k];
+            const T* w = wd + ((size_t)e * width + c) * ff;
+            const float* a = as + (size_t)k * ff;
+            float acc = 0.0f;
+            for (int i = lane; i < ff; i += 32) acc = fmaf(a[i], to_f32<T>(w[i]), acc);
+            total = fmaf(wts[(size_t)t * top + k], warp_sum(acc), total);
+        }
+        if (lane == 0) y[(size_t)t * width + c] += total;
+    }
+}
+
+}  // namespace vk
+
+using namespace vk;
+
+// x [tokens][width] in dtype; wr float32 [E][width], br float32 [E] or null; ids int32 [tokens][top], wts float32 [tokens][top].
+VK_API int vk_experts_route(const void* x, int width, const float* wr, const float* br, int E, int top, int32_t* ids, float* wts, int tokens,
+                            int dtype, cudaStream_t stream) {
+    if (tokens <= 0) return VK_OK;
+    if (width <= 0 || E <= 0 || top <= 0 || top > E || top > 32) return VK_BAD_SHAPE;
+    const size_t smem = (size_t)E * sizeof(float);
+    if (smem > 48 * 1024) return VK_TOO_LARGE;
+    if (dtype == 0) return launch_dependent(experts_route_kernel<float>, dim3(tokens), dim3(128), smem, stream, (const float*)x, width, wr, br, E, top, ids, wts);
+    return launch_dependent(experts_route_kernel<__nv_bfloat16>, dim3(tokens), dim3(128), smem, stream, (const __nv_bfloat16*)x, width, wr, br, E, top,
+                            ids, wts);
+}
+
+// wgu [E][2 ff][width] (an expert's gate rows, then its up rows) in dtype; out [tokens * top][ff] in dtype.  act: 0 none, 1 gelu (erf),
+// 2 gelu (tanh), 3 silu.
+VK_API int vk_experts_gate_up(const void* x, int width, const void* wgu, int ff, int top, const int32_t* ids, int act, void* out, int tokens,
+                              int dtype, cudaStream_t stream) {
+    if (tokens <= 0) return VK_OK;
+    if (width <= 0 || ff <= 0 || top <= 0) return VK_BAD_SHAPE;
+    const size_t smem = (size_t)width * sizeof(float);
+    if (smem > 48 * 1024) return VK_TOO_LARGE;
+    int gy = (ff + 7) / 8;
+    if (gy > 64) gy = 64;
+    dim3 grid(tokens * top, gy);
+    if (dtype == 0)
+        return launch_dependent(experts_gate_up_kernel<float>, grid, dim3(256), smem, stream, (const float*)x, width, (const float*)wgu, ff, top, ids, act,
+                                (float*)out);
+    return launch_dependent(experts_gate_up_kernel<__nv_bfloat16>, grid, dim3(256), smem, stream, (const __nv_bfloat16*)x, width,
+                            (const __nv_bfloat16*)wgu, ff, top, ids, act, (__nv_bfloat16*)out);
+}
+
+// act [tokens * top][ff] and wd [E][width][ff] in dtype; y float32 [tokens][width] is added to.
+VK_API int vk_experts_down(const void* act, int ff, const void* wd, int width, int top, const int32_t* ids, const float* wts, float* y, int tokens,
+                           int dtype, cudaStream_t stream) {
+    if (tokens <= 0) return VK_OK;
+    if (width <= 0 || ff <= 0 || top <= 0) return VK_BAD_SHAPE;
+    const size_t smem = (size_t)top * ff * sizeof(float);
+    if (smem > 48 * 1024) return VK_TOO_LARGE;
+    int gy = (width + 7) / 8;
+    if (gy > 64) gy = 64;
+    dim3 grid(tokens, gy);
+    if (dtype == 0)
+        return launch_dependent(experts_down_kernel<float>, grid, dim3(256), smem, stream, (const float*)act, ff, (const float*)wd, width, top, ids, wts, y);
+    return launch_dependent(experts_down_kernel<__nv_bfloat16>, grid, dim3(256), smem, stream, (const __nv_bfloat16*)act, ff, (const __nv_bfloat16*)wd,
+                            width, top, ids, wts, y);
+}

@@ -1,0 +1,135 @@
+// Steps around the sublayers of a decoder whose norm sits on a sublayer's OUTPUT, and an embedding with a second, hashed row.
+//
+//  embed_hashed       x[t] = E[id_t] + B[row_t];  row_t = (id_(t-1) a + id_t b) mod n, and row n for a request's first token.  The token
+//                     before a step's first one is a word of the request's state slot; the block of a segment's first token reads
+//                     it and then writes the segment's last token there (nobody else touches the word).
+//  residual_norm_step x[t] += m * (y[t] / sqrt(mean(y[t]^2) + eps)) * w;  y[t] <- 0;  xc[t] <- x[t] in the compute dtype (if asked).
+//                     Without w nothing is added: y is zeroed and xc written, which is how a pass begins.
+//                     One block a row; what a sublayer ADDED into the zeroed y is normed, scaled and summed into the float32
+//                     residual row, y is zero again for the next sublayer, and the next sublayer's input is written.
+//  glu_clamped        out = g' sigmoid(alpha g') (u' + 1),  g' = min(g, L),  u' = clamp(u, -L, L);  gu [T, 2I] -> out [T, I].
+//
+// All arithmetic is float32; accurate expf, division and sqrtf.
+#include "common.cuh"
+
+namespace vk {
+
+template <typename T>
+__global__ void __launch_bounds__(256) embed_hashed_kernel(const T* __restrict__ table, const T* __restrict__ second, const int32_t* __restrict__ ids,
+                                                           const int32_t* __restrict__ positions, const int32_t* __restrict__ token_seg,
+                                                           const int32_t* __restrict__ seg_starts, const int32_t* __restrict__ seg_slots,
+                                                           int32_t* __restrict__ last_token, float* __restrict__ x, T* __restrict__ xc, int hidden,
+                                                           int vocab, int buckets, int mul_prev, int mul_cur) {
+    __shared__ int row_s;
+    dependency_wait();
+    let_dependents_start();
+    const int t = blockIdx.x;
+    int id = ids[t];
+    if (id < 0 || id >= vocab) id = 0;          // the host has checked the range; never read outside the table
+    if (threadIdx.x == 0) {
+        const int seg = token_seg[t];
+        const int first = seg_starts[seg], slot = seg_slots[seg];
+        int prev = 0;
+        if (t > first) prev = ids[t - 1];
+        else if (slot >= 0) {
+            prev = last_token[slot];
+            int last = ids[seg_starts[seg + 1] - 1];
+            last_token[slot] = last;
+        }
+        if (prev < 0 || prev >= vocab) prev = 0;
+        row_s = positions[t] == 0 ? buckets : (int)(((long long)prev * mul_prev + (long long)id * mul_cur) % buckets);
+    }
+    __syncthreads();
+    const T* a = table + (size_t)id * hidden;
+    float* out = x + (size_t)t * hidden;
+    if (second) {
+        const T* b = second + (size_t)row_s * hidden;
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+            const float v = to_f32<T>(a[i]) + to_f32<T>(b[i]);
+            out[i] = v;
+            if (xc) xc[(size_t)t * hidden + i] = from_f32<T>(v);
+        }
+    } else {
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+            const float v = to_f32<T>(a[i]);
+            out[i] = v;
+            if (xc) xc[(size_t)t * hidden + i] = from_f32<T>(v);
+        }
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) residual_norm_step_kernel(float* __restrict__ x, float* __restrict__ y, const float* __restrict__ w,
+                                                                 T* __restrict__ xc, int n, float eps, float mult) {
+    __shared__ float scratch[32];
+    dependency_wait();
+    let_dependents_start();
+    const size_t base = (size_t)blockIdx.x * n;
+    if (!w) {                                   // the form that starts a pass: nothing is added
+        for (int i = threadIdx.x; i < n; i += blockDim.x) {
+            if (y) y[base + i] = 0.0f;
+            if (xc) xc[base + i] = from_f32<T>(x[base + i]);
+        }
+        return;
+    }
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) { const float v = y[base + i]; ss = fmaf(v, v, ss); }
+    ss = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float)n + eps);
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const float v = x[base + i] + mult * ((y[base + i] * inv) * w[i]);
+        x[base + i] = v;
+        y[base + i] = 0.0f;
+        if (xc) xc[base + i] = from_f32<T>(v);
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) glu_clamped_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter, float limit, float alpha) {
+    dependency_wait();
+    let_dependents_start();
+    const T* row = gu + (size_t)blockIdx.x * 2 * inter;
+    for (int i = threadIdx.x; i < inter; i += blockDim.x) {
+        const float g = fminf(to_f32<T>(row[i]), limit);
+        const float u = fminf(fmaxf(to_f32<T>(row[inter + i]), -limit), limit);
+        out[(size_t)blockIdx.x * inter + i] = from_f32<T>((g / (1.0f + expf(-alpha * g))) * (u + 1.0f));
+    }
+}
+
+}  // namespace vk
+
+using namespace vk;
+
+// table [vocab][hidden], second [buckets + 1][hidden] (null: no second row) in dtype; last_token int32 [slots] (may be null when
+// second is null); x float32 [tokens][hidden]; xc [tokens][hidden] in dtype or null.
+VK_API int vk_embed_hashed(const void* table, const void* second, const int32_t* ids, const int32_t* positions, const int32_t* token_seg,
+                           const int32_t* seg_starts, const int32_t* seg_slots, int32_t* last_token, float* x, void* xc, int tokens, int hidden,
+                           int vocab, int buckets, int mul_prev, int mul_cur, int dtype, cudaStream_t stream) {
+    if (tokens <= 0) return VK_OK;
+    if (hidden <= 0 || vocab <= 0 || (second && (buckets <= 0 || !last_token))) return VK_BAD_SHAPE;
+    if (dtype == 0)
+        return launch_dependent(embed_hashed_kernel<float>, dim3(tokens), dim3(256), 0, stream, (const float*)table, (const float*)second, ids,
+                                positions, token_seg, seg_starts, seg_slots, last_token, x, (float*)xc, hidden, vocab, buckets, mul_prev, mul_cur);
+    return launch_dependent(embed_hashed_kernel<__nv_bfloat16>, dim3(tokens), dim3(256), 0, stream, (const __nv_bfloat16*)table,
+                            (const __nv_bfloat16*)second, ids, positions, token_seg, seg_starts, seg_slots, last_token, x, (__nv_bfloat16*)xc,
+                            hidden, vocab, buckets, mul_prev, mul_cur);
+}
+
+// x, y float32 [rows][n]; w float32 [n]; xc [rows][n] in dtype, or null.
+VK_API int vk_residual_norm_step(float* x, float* y, const float* w, void* xc, int rows, int n, float eps, float mult, int dtype,
+                                 cudaStream_t stream) {
+    if (rows <= 0) return VK_OK;
+    if (n <= 0 || (w && !y)) return VK_BAD_SHAPE;
+    const int threads = n >= 1024 ? 256 : 128;
+    if (dtype == 0)
+        return launch_dependent(residual_norm_step_kernel<float>, dim3(rows), dim3(threads), 0, stream, x, y, w, (float*)xc, n, eps, mult);
+    return launch_dependent(residual_norm_step_kernel<__nv_bfloat16>, dim3(rows), dim3(threads), 0, stream, x, y, w, (__nv_bfloat16*)xc, n, eps, mult);
+}
+
+VK_API int vk_glu_clamped(const void* gu, void* out, int tokens, int inter, float limit, float alpha, int dtype, cudaStream_t stream) {
+    if (tokens <= 0) return VK_OK;
+    if (inter <= 0 || !(limit > 0.0f)) return VK_BAD_SHAPE;
+    if (dtype == 0) return launch_dependent(glu_clamped_kernel<float>, dim3(tokens), dim3(256), 0, stream, (const float*)gu, (float*)out, inter, limit, alpha);
+    return launch_dependent(glu_clamped_kernel<__nv_bfloat16>, dim3(tokens), dim3(256), 0, stream, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, inter,
+                            limit, alpha);
+}

@@ -6,10 +6,16 @@ writes it.  A block may be named twice (its weights run twice, each run with a
 cache layer of its own unless told otherwise), and a run may read the cache
 layer that another run wrote (write_cache=False).  Cache layers are numbered
 0..num_caches-1; each gets what its mixer's cache_spec() asks for.
+
+A mixer may need a fixed-size state BESIDE its pages (the memory of a short
+convolution in front of an attention): it says so with state_spec(), and its
+run names a second cache layer (`state`) that holds it; the mixer then sees
+one view with both.  A token input with state_spec() (the token before a
+step's first one) gets a cache layer of its own behind all others.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass
+from dataclasses import dataclass, replace
 from typing import List, Optional, Sequence
 
 import torch
@@ -23,6 +29,7 @@ class LayerRun:
     block: int                  # index into DecoderModel.blocks
     cache: int                  # cache layer this run uses
     write_cache: bool = True    # False: read what another run of the step wrote
+    state: int = -1             # cache layer of the fixed-size state the mixer keeps beside its pages (-1: none)
 
 
 class DecoderModel:
@@ -35,18 +42,32 @@ class DecoderModel:
         self.embedding, self.blocks, self.schedule = embedding, list(blocks), list(schedule)
         self.final_norm, self.lm_head, self.position = final_norm, lm_head, position
         self.dtype, self.vocab_size, self.max_positions, self.config = dtype, vocab_size, max_positions, config
-        n_caches = 1 + max((r.cache for r in self.schedule), default=-1)
+        n_caches = 1 + max((max(r.cache, r.state) for r in self.schedule), default=-1)
         specs: List[CacheSpec] = [None] * n_caches
         writers = [0] * n_caches
         for run in self.schedule:
-            spec = self.blocks[run.block].mixer.cache_spec()
+            mixer = self.blocks[run.block].mixer
+            spec = mixer.cache_spec()
             if specs[run.cache] is not None and specs[run.cache] != spec:
                 raise ValueError(f"cache layer {run.cache} is used by mixers with different needs")
             specs[run.cache] = spec
             writers[run.cache] += bool(run.write_cache)
+            beside = mixer.state_spec() if hasattr(mixer, "state_spec") else None
+            if (beside is None) != (run.state < 0):
+                raise ValueError("a run names a state layer exactly when its mixer keeps a state beside its pages")
+            if beside is not None:
+                if specs[run.state] is not None or run.state == run.cache:
+                    raise ValueError(f"cache layer {run.state} holds one run's state and nothing else")
+                specs[run.state] = beside
+                writers[run.state] += 1
         for c, n in enumerate(writers):
             if specs[c] is not None and n != 1:
                 raise ValueError(f"cache layer {c} has {n} writers in the schedule; it needs exactly one")
+        self._input_state = -1
+        beside = embedding.state_spec() if hasattr(embedding, "state_spec") else None
+        if beside is not None:
+            self._input_state = len(specs)
+            specs.append(beside)
         self._cache_specs = specs
 
     def cache_specs(self) -> List[CacheSpec]:
@@ -73,11 +94,14 @@ class DecoderModel:
     def forward(self, ctx: StepContext, logit_rows: Optional[torch.Tensor], out: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
         """Run the batch; float32 logits [len(logit_rows), vocab] for the flat token indices in logit_rows
         (written into `out` when given, else into a new tensor)."""
-        x = self.embedding.forward(ctx)
+        ctx.extra["pass"] = ctx.extra.get("pass", 0) + 1        # parts that do something once a pass tell passes apart by this
+        x = self.embedding.forward(ctx) if self._input_state < 0 else self.embedding.forward(ctx, ctx.caches[self._input_state].state)
         if self.position is not None:
             self.position.on_embeddings(x, ctx)
         for i, run in enumerate(self.schedule):
             cache = ctx.caches[run.cache] if run.cache >= 0 else None
+            if run.state >= 0:
+                cache = replace(cache, state=ctx.caches[run.state].state)
             self.blocks[run.block].forward(x, ctx, cache, run.write_cache)
             if ctx.after_run is not None:
                 ctx.after_run(i)

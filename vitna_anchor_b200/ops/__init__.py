@@ -1193,3 +1193,195 @@ def linear_gated(x: torch.Tensor, w_gate_up: torch.Tensor, gu: torch.Tensor, out
                    "linear_tcgen05_gated")
             return out
     return act_mul(linear(x, w_gate_up, gu, LINEAR_SAME), out, kind)
+
+
+# ---------------------------------------------------------------------------
+# A decoder whose norm sits on a sublayer's output; an embedding with a second, hashed row; a clamped gated activation
+# ---------------------------------------------------------------------------
+
+def embed_hashed(table: torch.Tensor, second: Optional[torch.Tensor], ids: torch.Tensor, positions: torch.Tensor, token_seg: torch.Tensor,
+                 seg_starts: torch.Tensor, seg_slots: torch.Tensor, last_token: Optional[torch.Tensor], x: torch.Tensor,
+                 xc: Optional[torch.Tensor], buckets: int = 0, mul_prev: int = 0, mul_cur: int = 0) -> torch.Tensor:
+    """x[t] = table[id_t] + second[(id_(t-1) * mul_prev + id_t * mul_cur) mod buckets] (row `buckets` at position 0), float32; xc the same in
+    the tables' dtype.  last_token int32 [slots]: the token before a step's first one, read and moved on by the kernel."""
+    _req(table, "table", dims=2); _req(ids, "ids", torch.int32, 1); _req(x, "x", torch.float32, 2)
+    T, W = x.shape
+    if table.shape[1] != W or ids.shape[0] < T or positions.shape[0] < T or token_seg.shape[0] < T:
+        raise KernelError("embed_hashed: shapes do not fit")
+    if second is not None:
+        _req(second, "second", table.dtype, 2); _req(last_token, "last_token", torch.int32)
+        if second.shape != (buckets + 1, W) or buckets < 1:
+            raise KernelError("embed_hashed: the second table is not [buckets + 1, width]")
+    if xc is not None:
+        _req(xc, "xc", table.dtype, 2)
+        if xc.shape != (T, W):
+            raise KernelError("embed_hashed: xc is not [tokens, width]")
+    _check(lib().vk_embed_hashed(_p(table), _p(second), _p(ids), _p(positions), _p(token_seg), _p(seg_starts), _p(seg_slots), _p(last_token),
+                                 _p(x), _p(xc), T, W, table.shape[0], buckets, mul_prev, mul_cur, _dt(table), _stream()), "embed_hashed")
+    return x
+
+
+def residual_norm_step(x: torch.Tensor, y: Optional[torch.Tensor], w: Optional[torch.Tensor], xc: Optional[torch.Tensor], eps: float = 0.0,
+                       mult: float = 1.0) -> torch.Tensor:
+    """x += mult * (y / sqrt(mean(y^2) + eps)) * w, y <- 0, xc <- x in xc's dtype; all float32 [T, W] but xc.  With w None nothing is
+    added (y is only zeroed and xc written): the form that starts a pass."""
+    _req(x, "x", torch.float32, 2)
+    T, W = x.shape
+    if y is not None:
+        _req(y, "y", torch.float32, 2)
+        if y.shape != (T, W):
+            raise KernelError("residual_norm_step: y is not x's shape")
+    if w is not None:
+        _req(w, "w", torch.float32, 1)
+        if w.shape[0] != W or y is None:
+            raise KernelError("residual_norm_step: the weight does not fit the rows")
+    if xc is not None:
+        _req(xc, "xc", dims=2)
+        if xc.shape != (T, W):
+            raise KernelError("residual_norm_step: xc is not x's shape")
+    _check(lib().vk_residual_norm_step(_p(x), _p(y), _p(w), _p(xc), T, W, ctypes.c_float(eps), ctypes.c_float(mult),
+                                       0 if xc is None else _dt(xc), _stream()), "residual_norm_step")
+    return x
+
+
+def glu_clamped(gu: torch.Tensor, out: torch.Tensor, limit: float, alpha: float) -> torch.Tensor:
+    """out = g' sigmoid(alpha g') (u' + 1), g' = min(gu[:, :I], limit), u' = clamp(gu[:, I:], -limit, limit)."""
+    _req(gu, "gu", dims=2); _req(out, "out", gu.dtype, 2)
+    if gu.shape[1] != 2 * out.shape[1] or gu.shape[0] != out.shape[0]:
+        raise KernelError("glu_clamped: gu is not [tokens, 2 * intermediate]")
+    _check(lib().vk_glu_clamped(_p(gu), _p(out), out.shape[0], out.shape[1], ctypes.c_float(limit), ctypes.c_float(alpha), _dt(gu), _stream()),
+           "glu_clamped")
+    return out
+
+
+# ---------------------------------------------------------------------------
+# Differential attention: what lies around its products and the attention itself
+# ---------------------------------------------------------------------------
+
+def diff_attn_channels(H: int, G: int, dim: int, vdim: int, own_kv: bool) -> int:
+    """Channels that pass the short convolution: q, and k and v where the layer has its own."""
+    return H * 2 * dim + (G * 2 * dim + G * vdim if own_kv else 0)
+
+
+def diff_attn_prepare(proj: torch.Tensor, bias: Optional[torch.Tensor], conv_w: Optional[torch.Tensor], taps: int, tail: Optional[torch.Tensor],
+                      ctx, qn_w: torch.Tensor, kn_w: Optional[torch.Tensor], eps: float, freq: Optional[torch.Tensor], mag: float, dims: int,
+                      H: int, G: int, dim: int, vdim: int, own_kv: bool, slot_mapping: Optional[torch.Tensor], cache_layer: Optional[torch.Tensor],
+                      page_size: int, qout: torch.Tensor, out_bias: Optional[torch.Tensor] = None, y: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """From the float32 rows of the first product [q | k | v | ...]: bias, short convolution (memory in `tail` [slots, taps-1, C]), norm per
+    head and map, rotation; q to qout [T, 2H * dim] (order [key head][map][query head of the group]), k and v into the cache slots.
+    `ctx` gives token_seg, seg_starts, seg_slots and positions.  out_bias (float32 [width]) is added into y's rows."""
+    _req(proj, "proj", torch.float32, 2); _req(qn_w, "qn_w", torch.float32, 1); _req(qout, "qout", dims=2)
+    T, N = proj.shape
+    C = diff_attn_channels(H, G, dim, vdim, own_kv)
+    if qout.shape != (T, 2 * H * dim) or qn_w.shape[0] != dim or N < C or (dims and (freq is None or freq.shape[0] * 2 != dims)):
+        raise KernelError("diff_attn_prepare: shapes do not fit")
+    if bias is not None:
+        _req(bias, "bias", torch.float32, 1)
+        if bias.shape[0] < C:
+            raise KernelError("diff_attn_prepare: the bias is shorter than the channels")
+    if conv_w is not None:
+        _req(conv_w, "conv_w", torch.float32, 2)
+        if conv_w.shape != (C, taps):
+            raise KernelError("diff_attn_prepare: the convolution's weights are not [channels, taps]")
+        if taps > 1:
+            _req(tail, "tail", torch.float32)
+            if tail[0].numel() != (taps - 1) * C:
+                raise KernelError("diff_attn_prepare: the convolution's memory is not [slots, taps - 1, channels]")
+    if own_kv:
+        _req(kn_w, "kn_w", torch.float32, 1); _req(slot_mapping, "slot_mapping", torch.int32, 1); _req(cache_layer, "cache_layer", qout.dtype)
+        if kn_w.shape[0] != dim or slot_mapping.shape[0] < T or _page_size_of(cache_layer, 2 * G, dim, vdim, 2) != page_size:
+            raise KernelError("diff_attn_prepare: the cache layer does not fit the head counts")
+    if out_bias is not None:
+        _req(out_bias, "out_bias", torch.float32, 1); _req(y, "y", torch.float32, 2)
+        if y.shape != (T, out_bias.shape[0]):
+            raise KernelError("diff_attn_prepare: the output bias does not fit y")
+    _check(lib().vk_diff_attn_prepare(_p(proj), N, _p(bias), _p(conv_w), taps, _p(tail if conv_w is not None and taps > 1 else None),
+                                      _p(ctx.token_seg), _p(ctx.seg_starts), _p(ctx.seg_slots), _p(ctx.positions), _p(qn_w),
+                                      _p(kn_w if own_kv else None), ctypes.c_float(eps), _p(freq), ctypes.c_float(mag), dims, H, G, dim, vdim,
+                                      int(own_kv), _p(slot_mapping if own_kv else None), _p(cache_layer if own_kv else None), page_size, _p(qout),
+                                      _p(out_bias), _p(y if out_bias is not None else None), 0 if out_bias is None else out_bias.shape[0], T,
+                                      _dt(qout), _stream()), "diff_attn_prepare")
+    return qout
+
+
+def diff_attn_combine(att: torch.Tensor, proj: torch.Tensor, gate_off: int, lam: float, diff: float, eps: float, H: int, G: int, vdim: int,
+                      out: torch.Tensor, bias: Optional[torch.Tensor], taps: int, channels: int, tail: Optional[torch.Tensor], ctx) -> torch.Tensor:
+    """out [T, H * vdim] = rms-normed (a1 - lam * a2) * (1 - diff) * sigmoid(gate) per head, from att [T, 2H * vdim] in the order
+    diff_attn_prepare wrote the queries; moves the convolution's memory on for every segment."""
+    _req(att, "att", dims=2); _req(proj, "proj", torch.float32, 2); _req(out, "out", att.dtype, 2)
+    T, N = proj.shape
+    if att.shape != (T, 2 * H * vdim) or out.shape != (T, H * vdim) or gate_off + H * vdim > N:
+        raise KernelError("diff_attn_combine: shapes do not fit")
+    use_tail = tail is not None and taps > 1
+    _check(lib().vk_diff_attn_combine(_p(att), _p(proj), N, gate_off, ctypes.c_float(lam), ctypes.c_float(diff), ctypes.c_float(eps), H, G, vdim,
+                                      _p(out), _p(bias), taps, channels, _p(tail if use_tail else None), _p(ctx.token_seg), _p(ctx.seg_starts),
+                                      _p(ctx.seg_slots), T, _dt(att), _stream()), "diff_attn_combine")
+    return out
+
+
+# ---------------------------------------------------------------------------
+# The matrix memory with exponential gates
+# ---------------------------------------------------------------------------
+
+def mlstm_state_floats(H: int, dim: int, vdim: int) -> int:
+    """A slot's state: S [H, dim, vdim], n [H, dim], m [H]."""
+    return H * dim * vdim + H * dim + H
+
+
+def mlstm_max_dim() -> int:
+    return int(lib().vk_mlstm_max_dim())
+
+
+def mlstm(proj: torch.Tensor, gate_bias: torch.Tensor, cap: float, norm_w: torch.Tensor, eps: float, ctx, state: torch.Tensor,
+          o: torch.Tensor, out: torch.Tensor, H: int, dim: int, vdim: int) -> torch.Tensor:
+    """proj float32 [T, N] = q | k | v | gate | a | b; the recurrence token after token per segment from and into `state`
+    [slots, mlstm_state_floats]; out [T, H * vdim] = o / rms(o) * norm_w * sigmoid(gate) in out's dtype."""
+    _req(proj, "proj", torch.float32, 2); _req(gate_bias, "gate_bias", torch.float32, 1); _req(norm_w, "norm_w", torch.float32, 1)
+    _req(state, "state", torch.float32); _req(o, "o", torch.float32, 2); _req(out, "out", dims=2)
+    T, N = proj.shape
+    if (N < 2 * H * dim + 2 * H * vdim + 2 * H or gate_bias.shape[0] != 2 * H or norm_w.shape[0] != H * vdim or o.shape != (T, H * vdim)
+            or out.shape != (T, H * vdim) or state[0].numel() != mlstm_state_floats(H, dim, vdim)):
+        raise KernelError("mlstm: shapes do not fit the head counts")
+    _check(lib().vk_mlstm_recurrence(_p(proj), N, H, dim, vdim, _p(gate_bias), ctypes.c_float(cap), _p(ctx.seg_starts), _p(ctx.seg_slots),
+                                     _p(state), _p(o), ctx.num_segments, _stream()), "mlstm_recurrence")
+    _check(lib().vk_mlstm_gate(_p(o), _p(proj), N, 2 * H * dim + H * vdim, _p(norm_w), ctypes.c_float(eps), H, vdim, _p(out), T, _dt(out),
+                               _stream()), "mlstm_gate")
+    return out
+
+
+# ---------------------------------------------------------------------------
+# A routed feed-forward
+# ---------------------------------------------------------------------------
+
+_EPILOGUE_ACT = {"gelu": 1, "gelu_tanh": 2, "silu": 3}
+
+
+def experts_route(x: torch.Tensor, w_router: torch.Tensor, b_router: Optional[torch.Tensor], top: int, ids: torch.Tensor,
+                  wts: torch.Tensor) -> None:
+    """ids [T, top], wts [T, top]: the `top` largest of the float32 logits w_router x + b and the softmax over them alone."""
+    _req(x, "x", dims=2); _req(w_router, "w_router", torch.float32, 2); _req(ids, "ids", torch.int32, 2); _req(wts, "wts", torch.float32, 2)
+    T, W = x.shape
+    if w_router.shape[1] != W or ids.shape != (T, top) or wts.shape != (T, top) or (b_router is not None and b_router.shape != (w_router.shape[0],)):
+        raise KernelError("experts_route: shapes do not fit")
+    if b_router is not None:
+        _req(b_router, "b_router", torch.float32, 1)
+    _check(lib().vk_experts_route(_p(x), W, _p(w_router), _p(b_router), w_router.shape[0], top, _p(ids), _p(wts), T, _dt(x), _stream()), "experts_route")
+
+
+def experts_apply(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, act_buf: torch.Tensor,
+                  y: torch.Tensor, activation: str = "silu") -> torch.Tensor:
+    """y [T, W] (float32) += sum_k wts[t, k] W_down,e (act(W_gate,e x) * W_up,e x), e = ids[t, k]; w_gate_up [E, 2 ff, W], w_down [E, W, ff]
+    in x's dtype; act_buf [T * top, ff] in x's dtype."""
+    _req(x, "x", dims=2); _req(w_gate_up, "w_gate_up", x.dtype, 3); _req(w_down, "w_down", x.dtype, 3); _req(y, "y", torch.float32, 2)
+    _req(act_buf, "act_buf", x.dtype, 2)
+    T, W = x.shape
+    E, two_ff, _ = w_gate_up.shape
+    ff, top = two_ff // 2, ids.shape[1]
+    if w_gate_up.shape != (E, 2 * ff, W) or w_down.shape != (E, W, ff) or y.shape != (T, W) or act_buf.shape != (T * top, ff):
+        raise KernelError("experts_apply: shapes do not fit")
+    if activation not in _EPILOGUE_ACT:
+        raise KernelError(f"experts_apply: {activation!r} is not one of {sorted(_EPILOGUE_ACT)}")
+    _check(lib().vk_experts_gate_up(_p(x), W, _p(w_gate_up), ff, top, _p(ids), _EPILOGUE_ACT[activation], _p(act_buf), T, _dt(x), _stream()),
+           "experts_gate_up")
+    _check(lib().vk_experts_down(_p(act_buf), ff, _p(w_down), W, top, _p(ids), _p(wts), _p(y), T, _dt(x), _stream()), "experts_down")
+    return y

@@ -128,7 +128,11 @@ class Norm(Part):
 
 
 class TokenInput(Part):
-    """What turns a batch's token ids into the float32 residual stream."""
+    """What turns a batch's token ids into the float32 residual stream.  An input that carries something from step to step
+    says so with state_spec() (a StateSpec) and is then called as forward(ctx, state), state [slots, *shape]."""
+
+    def state_spec(self):
+        return None
 
     def forward(self, ctx: StepContext) -> torch.Tensor:
         """-> float32 [T, hidden]"""
@@ -166,6 +170,11 @@ class Mixer(Part):
     """Mixes information between positions of a request (attention, or anything with a state)."""
 
     def cache_spec(self) -> CacheSpec:
+        return None
+
+    def state_spec(self):
+        """A StateSpec for a fixed-size state that the mixer keeps BESIDE the pages cache_spec() asks for (None: none).  The
+        run of such a mixer names a second cache layer for it, and forward() finds it in cache.state."""
         return None
 
     def forward(self, xn: torch.Tensor, ctx: StepContext, cache: Optional[LayerCacheView], residual: torch.Tensor,

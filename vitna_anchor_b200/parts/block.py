@@ -1,10 +1,15 @@
 """Pre-norm residual block: x += mixer(norm1(x)); x += feed_forward(norm2(x))
-(engine/src/model.c:906-972)."""
+(engine/src/model.c:906-972).
+
+Output-norm residual block: x += m * norm1(mixer(x)); x += m * norm2(feed_forward(x)): the sublayers read the residual
+stream as it is and the norm sits on what they give."""
 from __future__ import annotations
 
 from typing import Optional
 
 import torch
+
+from .. import ops
 
 from ..cache.manager import LayerCacheView
 from .base import Block, FeedForward, Mixer, Norm, StepContext
@@ -31,3 +36,41 @@ class PreNormBlock(Block):
             self.ffn.forward(x, ctx, x, norm=self.ffn_norm)
         else:
             self.ffn.forward(self.ffn_norm.forward(x, ctx, "block.xn"), ctx, x)
+
+
+class OutputNormBlock(Block):
+    """x <- x + mult * norm(sublayer(x)) for the mixer and then (unless absent) the feed-forward; the norms have the RMS form.
+
+    The sublayers keep the framework's contract (they ADD their result into a float32 buffer), only that the buffer is not
+    the residual stream but a zeroed row y; one kernel then norms y, scales it, sums it into the float32 residual row, zeroes
+    y again and writes the next sublayer's input in the compute dtype.  The first block of a pass writes that input and zeroes
+    y itself (a pass is numbered in ctx.extra["pass"] by the decoder), so a step that was given up half-way leaves nothing
+    behind.  In float32 the sublayers read the residual stream itself."""
+
+    def __init__(self, mixer_norm: Norm, mixer: Mixer, ffn_norm: Optional[Norm] = None, ffn: Optional[FeedForward] = None, mult: float = 1.0):
+        if (ffn is None) != (ffn_norm is None):
+            raise ValueError("a feed-forward and its norm come together")
+        if mixer_norm.as_rms() is None or (ffn_norm is not None and ffn_norm.as_rms() is None):
+            raise ValueError("the norms on the sublayers' outputs have the RMS form")
+        self.mixer_norm, self.mixer, self.ffn_norm, self.ffn, self.mult = mixer_norm, mixer, ffn_norm, ffn, float(mult)
+
+    def tensors(self):
+        return [t for p in (self.mixer_norm, self.mixer, self.ffn_norm, self.ffn) if p is not None for t in p.tensors()]
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache: Optional[LayerCacheView], write_cache: bool = True) -> None:
+        T, W, ws = ctx.num_tokens, x.shape[1], ctx.workspace
+        y = ws.flat(f"outnorm.y/{W}", ws.max_tokens * W, torch.float32, zero=True)[:T * W].view(T, W)
+        xc = x if ctx.dtype == torch.float32 else ws.rows("outnorm.xc", T, W, ctx.dtype)
+        copy = None if xc is x else xc
+        this_pass = ctx.extra.get("pass", 0)
+        if ctx.extra.get("outnorm.begun") != this_pass:
+            ops.residual_norm_step(x, y, None, copy)
+            ctx.extra["outnorm.begun"] = this_pass
+        self.mixer.forward(xc, ctx, cache, y, write_cache)
+        w, eps = self.mixer_norm.as_rms()
+        ops.residual_norm_step(x, y, w, copy, eps, self.mult)
+        if self.ffn is None:
+            return
+        self.ffn.forward(xc, ctx, y)
+        w, eps = self.ffn_norm.as_rms()
+        ops.residual_norm_step(x, y, w, copy, eps, self.mult)

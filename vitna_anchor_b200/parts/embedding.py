@@ -70,6 +70,35 @@ class ScaledEmbedding(TokenInput):
         return ops.embed_scaled(self.table, ctx.tokens, ctx.positions, self.positions, self.scale, x, self.copies)
 
 
+class HashedPairEmbedding(TokenInput):
+    """x = the token's row + a row of a second table chosen by a hash of the previous and the current token:
+    row (prev * mul_prev + cur * mul_cur) mod buckets, and row `buckets` (the last) for a request's first token.  The token
+    before a step's first one is one int32 word of the request's state slot (state_spec), moved on by the kernel."""
+
+    def __init__(self, vocab: int, hidden: int, table: torch.Tensor, second: torch.Tensor, buckets: int, mul_prev: int, mul_cur: int):
+        if table.shape != (vocab, hidden) or second.shape != (buckets + 1, hidden) or buckets < 1:
+            raise ValueError("the embedding tables do not fit the sizes")
+        self.vocab, self.hidden, self.buckets, self.mul_prev, self.mul_cur = vocab, hidden, int(buckets), int(mul_prev), int(mul_cur)
+        self.table, self.second = table.contiguous(), second.contiguous()
+
+    def tensors(self):
+        return [self.table, self.second]
+
+    def weight_bytes(self) -> int:
+        return 0                     # two rows per token are read, not the tables
+
+    def state_spec(self):
+        from ..cache.manager import StateSpec
+        return StateSpec((1,), torch.int32)
+
+    def forward(self, ctx: StepContext, state: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if state is None:
+            raise ValueError("the hashed embedding needs its word of the requests' state slots")
+        x = ctx.workspace.rows("x", ctx.num_tokens, self.hidden, torch.float32)
+        return ops.embed_hashed(self.table, self.second, ctx.tokens, ctx.positions, ctx.token_seg, ctx.seg_starts, ctx.seg_slots, state, x, None,
+                                self.buckets, self.mul_prev, self.mul_cur)
+
+
 class LMHead(LogitsOutput):
     def __init__(self, vocab: int, hidden: int, weight: torch.Tensor):
         if weight.shape != (vocab, hidden):

@@ -4,8 +4,16 @@ The gate and up matrices are stacked by rows so that one product reads xn once.
 
 With another activation than silu (`activation`, one of ops.ACTIVATIONS) it is the same gated form, y = W_down (act(W_gate xn) * (W_up xn)).
 
-The dense feed-forward: y = W_down act(W_up xn), act one of ops.ACTIVATIONS (the erf or the tanh form of gelu, silu)."""
+The dense feed-forward: y = W_down act(W_up xn), act one of ops.ACTIVATIONS (the erf or the tanh form of gelu, silu).
+
+The clamped gated feed-forward: g = min(W_gate xn, L), u = clamp(W_up xn, -L, L), y = W_down (g sigmoid(alpha g) (u + 1)).
+
+The routed feed-forward: a router chooses `top` of E small gated feed-forwards per token (the largest logits; their weights
+the softmax over the chosen logits alone); the weighted sum of their outputs, plus, if there is one, a feed-forward that every
+token uses."""
 from __future__ import annotations
+
+from typing import Optional
 
 import torch
 
@@ -67,3 +75,63 @@ class DenseMLP(FeedForward):
     def forward(self, xn: torch.Tensor, ctx: StepContext, residual: torch.Tensor, norm=None) -> None:
         act = ops.linear_act(xn, self.w_up, ctx.workspace.rows("ffn.act", ctx.num_tokens, self.intermediate, ctx.dtype), self.activation)
         ops.linear(act, self.w_down, residual, ops.LINEAR_ACC_F32)
+
+
+class ClampedGLU(FeedForward):
+    def __init__(self, hidden: int, intermediate: int, w_gate_up: torch.Tensor, w_down: torch.Tensor, limit: float, alpha: float = 1.702):
+        if w_gate_up.shape != (2 * intermediate, hidden) or w_down.shape != (hidden, intermediate):
+            raise ValueError("feed-forward weights do not fit the sizes")
+        if not limit > 0:
+            raise ValueError("the clamp's limit is positive")
+        self.hidden, self.intermediate, self.limit, self.alpha = hidden, intermediate, float(limit), float(alpha)
+        self.w_gate_up, self.w_down = w_gate_up.contiguous(), w_down.contiguous()
+
+    def tensors(self):
+        return [self.w_gate_up, self.w_down]
+
+    def forward(self, xn: torch.Tensor, ctx: StepContext, residual: torch.Tensor, norm=None) -> None:
+        T, ws = ctx.num_tokens, ctx.workspace
+        gu = ops.linear(xn, self.w_gate_up, ws.rows("ffn.gu", T, 2 * self.intermediate, ctx.dtype), ops.LINEAR_SAME)
+        act = ops.glu_clamped(gu, ws.rows("ffn.act", T, self.intermediate, ctx.dtype), self.limit, self.alpha)
+        ops.linear(act, self.w_down, residual, ops.LINEAR_ACC_F32)
+
+
+class RoutedExperts(FeedForward):
+    """w_router float32 [E, hidden] (+ b_router [E]); w_gate_up [E, 2 ff, hidden] (an expert's gate rows, then its up rows) and
+    w_down [E, hidden, ff] in the compute dtype; `shared`: a FeedForward every token passes as well (or None).  The router's
+    logits are float32 sums over the (compute dtype) input.  Which experts run never comes to the host: the kernels read the
+    choice on the device, so the part is replayed faithfully from a graph."""
+
+    def __init__(self, hidden: int, intermediate: int, experts: int, top: int, w_router: torch.Tensor, b_router: Optional[torch.Tensor],
+                 w_gate_up: torch.Tensor, w_down: torch.Tensor, shared: Optional[FeedForward] = None, activation: str = "silu"):
+        E = experts
+        if w_router.shape != (E, hidden) or w_gate_up.shape != (E, 2 * intermediate, hidden) or w_down.shape != (E, hidden, intermediate):
+            raise ValueError("the experts' weights do not fit the sizes")
+        if b_router is not None and b_router.shape != (E,):
+            raise ValueError("the router's bias does not fit the experts")
+        if not 1 <= top <= min(E, 32):
+            raise ValueError("a token uses between one and min(experts, 32) experts")
+        self.hidden, self.intermediate, self.E, self.top, self.activation, self.shared = hidden, intermediate, E, int(top), activation, shared
+        self.w_router = w_router.to(torch.float32).contiguous()
+        self.b_router = None if b_router is None else b_router.to(torch.float32).contiguous()
+        self.w_gate_up, self.w_down = w_gate_up.contiguous(), w_down.contiguous()
+
+    def tensors(self):
+        return [self.w_router, self.w_gate_up, self.w_down] + ([] if self.b_router is None else [self.b_router]) + \
+            ([] if self.shared is None else self.shared.tensors())
+
+    def weight_bytes(self) -> int:
+        """What one token reads: the router, its `top` experts, the shared feed-forward."""
+        one = (self.w_gate_up[0].numel() + self.w_down[0].numel()) * self.w_down.element_size()
+        return self.w_router.numel() * 4 + self.top * one + (0 if self.shared is None else self.shared.weight_bytes())
+
+    def forward(self, xn: torch.Tensor, ctx: StepContext, residual: torch.Tensor, norm=None) -> None:
+        T, ws = ctx.num_tokens, ctx.workspace
+        ids = ws.rows("moe.ids", T, self.top, torch.int32)
+        wts = ws.rows("moe.wts", T, self.top, torch.float32)
+        ops.experts_route(xn, self.w_router, self.b_router, self.top, ids, wts)
+        act = ws.flat(f"moe.act/{self.top}/{self.intermediate}", ws.max_tokens * self.top * self.intermediate, ctx.dtype)
+        ops.experts_apply(xn, self.w_gate_up, self.w_down, ids, wts, act[:T * self.top * self.intermediate].view(T * self.top, self.intermediate),
+                          residual, self.activation)
+        if self.shared is not None:
+            self.shared.forward(xn, ctx, residual)

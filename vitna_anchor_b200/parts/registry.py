@@ -32,10 +32,12 @@ def make_part(kind: str, name: str, **params):
 
 def _register_builtin() -> None:
     from .attention import PagedAttention
-    from .block import PreNormBlock
+    from .block import OutputNormBlock, PreNormBlock
+    from .diff_attention import DiffAttention
+    from .mlstm import MatrixLSTM
     from .delta import ChannelDeltaRule, GatedDeltaRule
     from .latent import LatentAttention
-    from .feed_forward import DenseMLP, SwiGLU
+    from .feed_forward import ClampedGLU, DenseMLP, RoutedExperts, SwiGLU
     from .hyper import HyperBlock
     from .norms import LayerNorm, RMSNorm
     from .rotary import NoPositionEncoding, Rotary
@@ -43,6 +45,10 @@ def _register_builtin() -> None:
     register_part("mixer", "gated_delta", GatedDeltaRule)
     register_part("mixer", "channel_delta", ChannelDeltaRule)
     register_part("mixer", "latent_attention", LatentAttention.from_matrices)
+    register_part("mixer", "diff_attention", DiffAttention)
+    register_part("mixer", "mlstm", MatrixLSTM)
+    register_part("feed_forward", "clamped_glu", ClampedGLU)
+    register_part("feed_forward", "routed_experts", RoutedExperts)
     register_part("feed_forward", "swiglu", SwiGLU)
     register_part("feed_forward", "gated", SwiGLU)           # the same part; `activation` chooses the gate's function
     register_part("feed_forward", "dense", DenseMLP)
@@ -51,6 +57,7 @@ def _register_builtin() -> None:
     register_part("position", "rotary", Rotary)
     register_part("position", "none", NoPositionEncoding)
     register_part("block", "pre_norm", PreNormBlock)
+    register_part("block", "output_norm", OutputNormBlock)
     register_part("block", "hyper", HyperBlock)
 
 
