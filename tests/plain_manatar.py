@@ -67,9 +67,11 @@ def sigmoid(z):
 
 
 def embed(cfg, w, ids):
-    big = cfg["embedding"]["bigram"]
-    n = big["buckets"]
     x = w["embed"][ids].copy()
+    big = (cfg.get("embedding") or {}).get("bigram")
+    if big is None:
+        return x
+    n = big["buckets"]
     for t, tok in enumerate(ids):
         row = n if t == 0 else (int(ids[t - 1]) * big["mul_prev"] + int(tok) * big["mul_cur"]) % n
         x[t] += w["bigram"][row]
@@ -78,6 +80,8 @@ def embed(cfg, w, ids):
 
 def short_conv(u, taps_w):
     """u [T, C], taps_w [C, taps]: y_t = sum_j w[:, j] u_(t - taps + 1 + j), zeros before the start."""
+    if taps_w is None:
+        return u
     T, C = u.shape
     taps = taps_w.shape[1]
     y = np.zeros_like(u)
@@ -105,6 +109,8 @@ def frequencies(rot):
 
 def rotate(x, rot):
     """x [T, n, d]: the first rot.dims values of every row turned pairwise (2i, 2i+1) by position * f_i."""
+    if not rot or not rot["dims"]:
+        return x
     f, mag = frequencies(rot)
     dims = rot["dims"]
     T = x.shape[0]
@@ -121,17 +127,17 @@ def attention_kv(w, p, m, h, eps):
     """The layer's keys (after convolution, norm and rotation) [T, G, 2, dim] and values (after convolution) [T, G, vdim]."""
     T = h.shape[0]
     G, dim, vdim = m["kv_heads"], m["dim"], m["vdim"]
-    k = short_conv(h @ w[p + "k"].T + w[p + "k.b"], w[p + "k.conv"]).reshape(T, G * 2, dim)
-    v = short_conv(h @ w[p + "v"].T + w[p + "v.b"], w[p + "v.conv"]).reshape(T, G, vdim)
-    k = rotate(rms(k, eps) * w[p + "k.norm"], m["rot"]).reshape(T, G, 2, dim)
+    k = short_conv(h @ w[p + "k"].T + w[p + "k.b"], w.get(p + "k.conv")).reshape(T, G * 2, dim)
+    v = short_conv(h @ w[p + "v"].T + w[p + "v.b"], w.get(p + "v.conv")).reshape(T, G, vdim)
+    k = rotate(rms(k, eps) * w[p + "k.norm"], m.get("rot")).reshape(T, G, 2, dim)
     return k, v
 
 
 def attention(w, p, m, h, eps, kv):
     T = h.shape[0]
     H, G, dim, vdim, diff = m["heads"], m["kv_heads"], m["dim"], m["vdim"], m["diff"]
-    q = short_conv(h @ w[p + "q"].T + w[p + "q.b"], w[p + "q.conv"]).reshape(T, H * 2, dim)
-    q = rotate(rms(q, eps) * w[p + "q.norm"], m["rot"]).reshape(T, H, 2, dim)
+    q = short_conv(h @ w[p + "q"].T + w[p + "q.b"], w.get(p + "q.conv")).reshape(T, H * 2, dim)
+    q = rotate(rms(q, eps) * w[p + "q.norm"], m.get("rot")).reshape(T, H, 2, dim)
     k, v = kv
     lam = math.exp(float(w[p + "lq1"] @ w[p + "lk1"])) - math.exp(float(w[p + "lq2"] @ w[p + "lk2"])) + diff
     mask = np.tril(np.ones((T, T), dtype=bool))
@@ -202,7 +208,7 @@ def moe_ff(w, p, mlp, h):
 def forward(cfg, w, ids, layers_out=None):
     """Logits [T, vocab] of one sequence; layers_out (a list) receives the residual stream after every layer."""
     ids = np.asarray(ids, dtype=np.int64)
-    eps, mult = cfg["norm"]["eps"], cfg["residual_mult"]
+    eps, mult = cfg["norm"]["eps"], cfg.get("residual_mult", 1.0)
     x = embed(cfg, w, ids)
     kvs = {}
     for i, layer in enumerate(cfg["layers"]):

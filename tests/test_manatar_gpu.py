@@ -1,0 +1,494 @@
+"""Manatar through the engine against the plain implementation (tests/plain_manatar.py), on small models of the tests' own.
+
+Every comparison is between the engine's step function (cache and state manager, kernels, CUDA graphs as in serving) and
+plain_manatar.forward on whole sequences.  float32 is held to 3e-5 of the logits' scale; bfloat16 to what 8 bits of mantissa
+cost on these sharp little models, and between ways of cutting the same request to less.
+"""
+import json
+import os
+import subprocess
+import sys
+from types import SimpleNamespace
+
+import numpy as np
+import pytest
+import torch
+
+import manatar_models as MM
+import plain_manatar as PM
+import replay_util as RU
+
+pytestmark = pytest.mark.gpu
+
+F32_TOL = 3e-5
+BF16_TOL = 1e-1
+BF16_CUT_TOL = 8e-2
+
+
+def _runner(model_dir, dtype, *, tokens=1024, page=16, slots=4, graphs=True):
+    from vitna_anchor_b200.engine.loading import load_model
+    from vitna_anchor_b200.engine.runner import ModelRunner
+    model = load_model(model_dir, dtype, "cuda")
+    return ModelRunner(model, page_size=page, num_pages=-(-tokens // page), max_requests=slots, max_batch_tokens=tokens,
+                       max_model_len=min(model.max_positions, tokens), device="cuda", cuda_graphs=graphs)
+
+
+def _play(runner, steps):
+    """steps as replay_util makes them -> {(request, position): logits row}; requests are opened at their first entry and closed
+    when a step ends them."""
+    from vitna_anchor_b200.engine.runner import StepEntry
+    got, at = {}, {}
+    for entries, end in steps:
+        for rid, _, _ in entries:
+            if not runner.cache.is_open(rid):
+                runner.open(rid)
+        logits = runner.step([StepEntry(rid, list(map(int, toks)), list(want)) for rid, toks, want in entries])
+        host = None if logits is None else logits.cpu().numpy()
+        runner.check(sync=True)
+        r = 0
+        for rid, toks, want in entries:
+            base = at.get(rid, 0)
+            for w in want:
+                got[(rid, base + w)] = host[r].copy()
+                r += 1
+            at[rid] = base + len(toks)
+        for rid in end:
+            runner.close(rid)
+            at.pop(rid, None)
+        runner.cache.check()
+    return got
+
+
+def _plain(model_dir, ids):
+    cfg, W = PM.read_model(model_dir)
+    return PM.forward(cfg, W, ids)
+
+
+def _worst(got, want_by_req, rms):
+    """The worst row's difference between the engine's and the plain logits.  float32 rows: the largest difference of one logit as
+    a fraction of the request's largest logit.  bfloat16 rows differ by rounding noise in every logit, so there (rms) the measure
+    is the root mean square of a row's differences over that of the request's logits."""
+    worst = 0.0
+    for (rid, pos), row in got.items():
+        ref = want_by_req[rid]
+        if rms:
+            worst = max(worst, float(np.sqrt(np.mean((row - ref[pos]) ** 2)) / np.sqrt(np.mean(ref ** 2))))
+        else:
+            worst = max(worst, float(np.abs(row - ref[pos]).max() / max(1.0, np.abs(ref).max())))
+    return worst
+
+
+def _ids(rng, vocab, n):
+    return [int(t) for t in rng.integers(0, vocab, n)]
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# each mechanism alone: models of one layer (two where a layer reads another's rows)
+# ---------------------------------------------------------------------------------------------------------------
+
+_A = MM.att
+ALONE = {
+    "embedding_pair": MM.config(40, 32, [MM.layer("mlstm", MM.mem(1, 8, 8, 5.0))], bigram=(7, 5, 3)),
+    "attention_bare": MM.config(40, 32, [MM.layer("attention", _A(2, 2, 8, 8, 0, 0.3, 0.4, None))], bigram=None),
+    "attention_conv": MM.config(40, 32, [MM.layer("attention", _A(2, 1, 16, 8, 4, 0.3, 0.3, None))], bigram=None),
+    "attention_rot": MM.config(40, 32, [MM.layer("attention", _A(3, 3, 16, 24, 0, 0.2, 0.3, MM.rot(40.0, 16)))], bigram=None),
+    "attention_rot_part": MM.config(40, 32, [MM.layer("attention", _A(4, 2, 32, 16, 2, 0.2, 0.2, MM.rot(1000.0, 12, (8.0, 32, 4.0, 1.0))))]),
+    "attention_kv_from": MM.config(40, 32, [MM.layer("attention", _A(2, 1, 16, 16, 3, 0.3, 0.3, MM.ROT_A)),
+                                            MM.layer("attention", _A(4, 1, 16, 16, 2, 0.6, 0.2, MM.ROT_A, kv_from=0))], mult=0.5),
+    "mlstm": MM.config(40, 32, [MM.layer("mlstm", MM.mem(2, 16, 24, 4.0))], bigram=None),
+    "mlstm_odd": MM.config(40, 24, [MM.layer("mlstm", MM.mem(3, 5, 37, 20.0))], bigram=None, mult=2.0),
+    "dense_ff": MM.config(40, 32, [MM.layer("mlstm", MM.mem(1, 8, 8, 5.0), MM.dense(72, 0.7))], bigram=None),
+    "experts_one": MM.config(40, 32, [MM.layer("mlstm", MM.mem(1, 8, 8, 5.0), MM.moe(24, 6, 1))], bigram=None),
+    "experts_some_shared": MM.config(40, 32, [MM.layer("mlstm", MM.mem(1, 8, 8, 5.0), MM.moe(16, 5, 3, 40))], bigram=None, mult=0.7),
+    "experts_all": MM.config(40, 32, [MM.layer("mlstm", MM.mem(1, 8, 8, 5.0), MM.moe(8, 3, 3))], bigram=None),
+}
+
+
+@pytest.mark.parametrize("name", sorted(ALONE))
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_each_mechanism_alone(tmp_path, name, dtype):
+    cfg = ALONE[name]
+    d = MM.write_model(tmp_path / name, cfg, MM.make_tensors(cfg, 5))
+    ids = _ids(np.random.default_rng(1), cfg["vocab"], 70)
+    ref = _plain(d, ids)
+    runner = _runner(d, dtype, tokens=128, page=8)
+    whole = _play(runner, RU.whole("a", ids))
+    one = _play(runner, RU.tail_one_by_one("b", ids, tail=69))        # the first token, then every token alone
+    two = _play(runner, RU.changing_portions("c", ids, sizes=(2,)))   # portions of two: shorter than the convolution's memory
+    rms = dtype == "bfloat16"
+    tol = BF16_TOL if rms else F32_TOL
+    for got, rid in ((whole, "a"), (one, "b"), (two, "c")):
+        assert len(got) == len(ids)
+        assert _worst(got, {rid: ref}, rms) < tol, rid
+
+
+def test_residual_stream_after_every_layer(tmp_path):
+    """The float32 engine's logits are right only if every layer is; this pins which layer a fault would be in: a model cut after
+    layer n must give head(norm(x_n)) of the plain implementation's residual stream."""
+    full = MM.CONFIGS["all"]
+    t = MM.make_tensors(full, 3)
+    ids = _ids(np.random.default_rng(5), full["vocab"], 40)
+    d = MM.write_model(tmp_path / "full", full, t)
+    cfg, W = PM.read_model(d)
+    streams = []
+    PM.forward(cfg, W, ids, layers_out=streams)
+    for n in range(1, len(full["layers"]) + 1):
+        cut = dict(full, layers=full["layers"][:n])
+        keep = {k: v for k, v in t.items() if not k.startswith("l") or int(k[1:].split(".")[0]) < n}
+        dn = MM.write_model(tmp_path / f"cut{n}", cut, keep)
+        want = (PM.rms(streams[n - 1], cfg["norm"]["eps"]) * W["final.norm"]) @ W["head"].T
+        got = _play(_runner(dn, "float32", tokens=64, page=8), RU.whole("a", ids))
+        assert _worst(got, {"a": want}, False) < F32_TOL, n
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# whole models: prompts, token by token, portions, mixed batches, pages and slots used again
+# ---------------------------------------------------------------------------------------------------------------
+
+@pytest.fixture(scope="module")
+def models(tmp_path_factory):
+    root = tmp_path_factory.mktemp("manatar")
+    out = {}
+    for i, name in enumerate(sorted(MM.CONFIGS)):
+        d = MM.make_model(root / name, name, seed=20 + i)
+        rng = np.random.default_rng(200 + i)
+        reqs = {f"r{k}": _ids(rng, MM.CONFIGS[name]["vocab"], n) for k, n in enumerate((150, 1, 37, 64, 91, 17))}
+        out[name] = (d, reqs, {r: _plain(d, ids) for r, ids in reqs.items()})
+    return out
+
+
+@pytest.mark.parametrize("name", sorted(MM.CONFIGS))
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_prompts_decoding_portions_and_mixed_batches(models, name, dtype):
+    d, reqs, ref = models[name]
+    rms = dtype == "bfloat16"
+    tol = BF16_TOL if rms else F32_TOL
+    cut_tol = BF16_CUT_TOL if rms else 1e-5
+    runner = _runner(d, dtype, tokens=384, page=8, slots=4)
+    whole = {}
+    for r, ids in reqs.items():
+        whole.update(_play(runner, RU.whole(r, ids)))
+    assert _worst(whole, ref, rms) < tol
+    runs = {}
+    # the last 40 tokens one by one (the one-token request is a prompt of one token)
+    runs["decode"] = {k: v for r, ids in reqs.items() for k, v in _play(runner, RU.tail_one_by_one(r, ids, tail=40)).items()}
+    # portions of changing sizes down to two tokens, cut inside pages
+    runs["portions"] = {k: v for r, ids in reqs.items()
+                        for k, v in _play(runner, RU.changing_portions(r, ids, sizes=(7, 2, 13, 3, 2, 29, 5, 2, 8, 11))).items()}
+    # up to four requests live, portions of some beside single tokens of others; six requests through four slots and a pool that
+    # holds fewer positions than the requests have in all
+    runs["mixed"] = _play(runner, RU.mixed(reqs, {r: max(1, len(ids) - 20) for r, ids in reqs.items()}, np.random.default_rng(3), live_max=4))
+    # one prompt in portions beside decoding requests
+    runs["beside"] = _play(runner, RU.mixed(reqs, {r: len(ids) // 2 for r, ids in reqs.items()}, np.random.default_rng(4), live_max=3,
+                                           portions=(2, 40), one_prompt_at_a_time=True))
+    for how, got in runs.items():
+        assert len(got) == sum(len(i) for i in reqs.values()), how
+        assert _worst(got, ref, rms) < tol, how
+        cut = _worst(got, {r: np.stack([whole[(r, p)] for p in range(len(ids))]) for r, ids in reqs.items()}, rms)
+        assert cut < cut_tol, (how, cut)
+    runner.cache.check()
+    assert all(f == p.num_pages for f, p in zip(runner.cache.free_pages(), runner.cache.tables.pools))     # every page came back
+
+
+def test_a_request_alone_and_beside_others_on_other_pages_and_slots(models):
+    """The same request first alone in a fresh engine, then as the fourth of four whose neighbours took the low pages and slots:
+    its keys, its matrix memories, its convolutions' memories and its previous token sit elsewhere, and slots that others left
+    are taken again."""
+    d, reqs, ref = models["all"]
+    ids = reqs["r4"]
+    alone = _play(_runner(d, "float32", tokens=512, page=8), RU.changing_portions("x", ids))
+    runner = _runner(d, "float32", tokens=512, page=8)
+    steps = [([("n0", reqs["r0"][:50], []), ("n1", reqs["r2"], []), ("n2", reqs["r3"][:9], [])], ["n1"])]      # n1's slot and pages come back
+    steps += [([("n0", reqs["r0"][50:52], []), ("x", ids[:30], range(30)), ("n2", reqs["r3"][9:10], [])], [])]
+    steps += [([("x", ids[30:31], [0]), ("n3", reqs["r5"], []), ("n0", reqs["r0"][52:53], [])], ["n3"])]
+    steps += [([("x", ids[31:], range(len(ids) - 31)), ("n2", reqs["r3"][10:11], [])], ["x", "n0", "n2"])]
+    beside = _play(runner, steps)
+    for k, row in alone.items():
+        assert np.abs(beside[k] - row).max() / np.abs(ref["r4"]).max() < 1e-5
+
+
+def test_a_slot_that_is_used_again_starts_from_nothing(models):
+    """One state slot: every request takes the slot the one before it left, with that request's matrix memory, running maximum,
+    convolution memories and previous token still in it."""
+    d, reqs, ref = models["odd"]
+    runner = _runner(d, "float32", tokens=256, page=8, slots=1)
+    for r in ("r0", "r2", "r1", "r5", "r2"):
+        got = _play(runner, RU.changing_portions(r, reqs[r], sizes=(5, 2, 31)))
+        assert _worst(got, ref, False) < F32_TOL, r
+
+
+def test_long_decoding(tmp_path):
+    """300 tokens one by one after a short prompt: the matrix memory and its running maximum are carried 300 times, the windows of
+    the convolutions move 300 times, the rotation passes 300 positions and the keys fill page after page."""
+    cfg = MM.CONFIGS["all"]
+    d = MM.make_model(tmp_path / "m", "all", seed=77)
+    ids = _ids(np.random.default_rng(8), cfg["vocab"], 310)
+    ref = _plain(d, ids)
+    for dtype, tol in (("float32", F32_TOL), ("bfloat16", BF16_TOL)):
+        got = _play(_runner(d, dtype, tokens=320, page=16), RU.tail_one_by_one("a", ids, tail=300))
+        assert _worst(got, {"a": ref}, dtype == "bfloat16") < tol
+
+
+def test_gates_that_grow_without_bound_stay_finite(tmp_path):
+    """Input gates at their cap and forget gates near one for 400 tokens: the running maximum climbs by about `cap` and stays there,
+    exp(-m) underflows toward zero, and the state must neither overflow nor lose the early tokens' share."""
+    cfg = MM.config(50, 32, [MM.layer("mlstm", MM.mem(2, 8, 8, 30.0))], bigram=None)
+    t = MM.make_tensors(cfg, 4)
+    t["l0.mix.i.b"][:] = 60.0
+    t["l0.mix.f.b"][:] = 60.0
+    d = MM.write_model(tmp_path / "m", cfg, t)
+    ids = _ids(np.random.default_rng(9), 50, 400)
+    ref = _plain(d, ids)
+    assert np.isfinite(ref).all()
+    got = _play(_runner(d, "float32", tokens=512, page=16), RU.changing_portions("a", ids, sizes=(100, 2, 1, 57)))
+    assert _worst(got, {"a": ref}, False) < F32_TOL
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# one key that must be found: far back, at the first position, on either side of a page's border
+# ---------------------------------------------------------------------------------------------------------------
+
+def _needle_model(tmp_path, dim=32, vocab=700, conv=0, rot=None):
+    """One attention layer, one head.  The token's embedding fills the first half of the width and the hashed pair's row the
+    second; the first score map has the normed first half itself as query and key (W_q = W_k = [I 0; 0 0], biases 0), the values
+    read the whole width.  So a token that comes twice scores dim * scale against its first coming and about sqrt(dim) * scale
+    against all others, and the last token's first map is half the value of ONE far key, which depends on that key's
+    predecessor, and half its own.  The second map has zero queries and spreads evenly.  A wrong page, slot or offset returns
+    another token's value.  With a convolution, the last tap of q and k is 1 and the others small; with a rotation, only a few of
+    the head's values turn."""
+    width = 2 * dim
+    cfg = MM.config(vocab, width, [MM.layer("attention", MM.att(1, 1, dim, dim, conv, 0.3, 1.0, rot))], bigram=(997, 31, 7))
+    t = MM.make_tensors(cfg, 3)
+    t["embed"][:, dim:] = 0.0
+    t["bigram"][:, :dim] = 0.0
+    eye = np.zeros((2 * dim, width), dtype=np.float32)
+    eye[:dim, :dim] = np.eye(dim)
+    t["l0.mix.q"], t["l0.mix.k"] = eye.copy(), eye.copy()
+    for n in ("q", "k", "v"):
+        t[f"l0.mix.{n}.b"][:] = 0.0
+        if conv and n != "v":
+            t[f"l0.mix.{n}.conv"][:, :-1] *= 0.05
+            t[f"l0.mix.{n}.conv"][:, -1] = 1.0
+    t["l0.mix.q.norm"][:] = 1.0
+    t["l0.mix.k.norm"][:] = 1.0
+    t["l0.mix.v"] *= 3.0
+    return MM.write_model(tmp_path / f"needle{conv}", cfg, t, dtype=torch.float32), cfg
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("conv,rot", [(0, None), (3, MM.rot(10000.0, 4))])
+def test_a_far_key_is_found_wherever_it_lies(tmp_path, dtype, conv, rot):
+    d, cfg = _needle_model(tmp_path, conv=conv, rot=rot)
+    rng = np.random.default_rng(0)
+    n, page = 600, 16
+    base = [int(t) for t in rng.permutation(cfg["vocab"])[:n]]            # all different
+    c, W = PM.read_model(d)
+    runner = _runner(d, dtype, tokens=640, page=page)
+    rms = dtype == "bfloat16"
+    for place in (0, 1, 3, page - 1, page, page + 1, 255, 256, 257, n - 3):
+        ids = base[:n - 1] + [base[place]]                               # the last token repeats the one at `place`
+        ref = PM.forward(c, W, ids)
+        if not conv:
+            # the test is sharp: in the plain implementation the far key and the last token's own have nearly all the weight
+            x = PM.rms(W["embed"][ids][:, :32], c["norm"]["eps"])
+            s = x @ x[-1]
+            e = np.exp(s - s.max())
+            assert e[place] / e.sum() > 0.45 and e[place] / e.sum() + e[-1] / e.sum() > 0.95
+        # and it shows in the logits: with the far key's token changed, the last row differs by a thousand float32 tolerances
+        other = list(ids)
+        other[place] = next(t for t in range(cfg["vocab"]) if t not in ids)
+        moved = PM.forward(c, W, other)[-1] - ref[-1]
+        assert np.sqrt(np.mean(moved ** 2)) / np.sqrt(np.mean(ref ** 2)) > 1000 * F32_TOL, place
+        tol = BF16_TOL if rms else F32_TOL
+        for how, steps in (("prompt", RU.whole("a", ids)), ("decoded", RU.tail_one_by_one("a", ids, tail=2)),
+                           ("portions", RU.changing_portions("a", ids, sizes=(250, 5, 2, 100)))):
+            got = _play(runner, steps)
+            last = {k: v for k, v in got.items() if k[1] == n - 1}
+            assert _worst(last, {"a": ref}, rms) < tol, (place, how)
+
+
+def test_the_second_map_is_subtracted(tmp_path):
+    """A layer whose two maps see the same scores gives (1 - lambda) a; lambda is made large by its four vectors, so that a
+    combine step that forgot the second map, or took `diff` for lambda, is far off."""
+    cfg = MM.config(60, 32, [MM.layer("attention", MM.att(2, 1, 8, 16, 2, 0.35, 0.5, MM.rot(100.0, 8)))], bigram=None)
+    t = MM.make_tensors(cfg, 6)
+    t["l0.mix.lq1"][:], t["l0.mix.lk1"][:] = 0.5, 0.5                   # exp(2) - exp(-1) + 0.35
+    t["l0.mix.lq2"][:], t["l0.mix.lk2"][:] = 0.25, -0.5
+    d = MM.write_model(tmp_path / "m", cfg, t)
+    ids = _ids(np.random.default_rng(3), 60, 48)
+    ref = _plain(d, ids)
+    t2 = dict(t)
+    t2["l0.mix.lq1"] = np.zeros_like(t["l0.mix.lq1"])
+    d2 = MM.write_model(tmp_path / "m2", cfg, t2)
+    assert np.abs(_plain(d2, ids) - ref).max() > 0.05 * np.abs(ref).max()      # lambda matters to the logits
+    got = _play(_runner(d, "float32", tokens=64, page=8), RU.tail_one_by_one("a", ids, tail=20))
+    assert _worst(got, {"a": ref}, False) < F32_TOL
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# kernels alone
+# ---------------------------------------------------------------------------------------------------------------
+
+def _dev(a, dtype=torch.float32):
+    return torch.tensor(np.asarray(a), dtype=dtype, device="cuda")
+
+
+def test_the_matrix_memory_kernel_against_the_recurrence_written_out():
+    """Segments of unequal length on scattered slots, a second step that continues from the state of the first, a padding segment
+    without a slot; key sizes that are no multiple of four and value sizes that are no multiple of 32."""
+    from vitna_anchor_b200 import ops
+    rng = np.random.default_rng(5)
+    for (H, dim, vdim, cap) in ((2, 16, 32, 8.0), (3, 5, 37, 2.0), (1, 64, 64, 15.0), (2, 130, 24, 4.0), (4, 256, 8, 30.0)):
+        N = 2 * H * dim + 2 * H * vdim + 2 * H
+        lens1, lens2, slots = [5, 1, 19], [1, 7, 2], [3, 0, 2]
+        bias, nw = rng.standard_normal(2 * H), 1 + 0.1 * rng.standard_normal(H * vdim)
+        proj_all = [rng.standard_normal((l1 + l2, N)) * np.concatenate([np.full(2 * H * dim + 2 * H * vdim, 1.0), np.full(2 * H, 3.0)])
+                    for l1, l2 in zip(lens1, lens2)]
+        state = torch.zeros(4, ops.mlstm_state_floats(H, dim, vdim), device="cuda")
+        state[1] = 7.0                                                   # a slot nobody holds: must stay as it is
+        outs = [[] for _ in lens1]
+        for step, lens in enumerate((lens1, lens2)):
+            T = sum(lens)
+            rows = np.concatenate([p[(0 if step == 0 else lens1[i]):(lens1[i] if step == 0 else None)] for i, p in enumerate(proj_all)])
+            lens_p, slots_p = lens + [0], slots + [-1]                   # and an empty segment without a slot
+            ctx = SimpleNamespace(seg_starts=_dev(np.concatenate([[0], np.cumsum(lens_p)]), torch.int32), seg_slots=_dev(slots_p, torch.int32),
+                                  num_segments=len(lens_p))
+            out = torch.empty(T, H * vdim, device="cuda")
+            ops.mlstm(_dev(rows), _dev(bias), cap, _dev(nw), 1e-5, ctx, state, torch.empty(T, H * vdim, device="cuda"), out, H, dim, vdim)
+            o = out.cpu().numpy()
+            at = 0
+            for i, n in enumerate(lens):
+                outs[i].append(o[at:at + n])
+                at += n
+        assert float((state[1] - 7.0).abs().max()) == 0.0
+        for i, p in enumerate(proj_all):
+            T = len(p)
+            q, k = p[:, :H * dim].reshape(T, H, dim) * dim ** -0.5, p[:, H * dim:2 * H * dim].reshape(T, H, dim)
+            v = p[:, 2 * H * dim:2 * H * dim + H * vdim].reshape(T, H, vdim)
+            gate = p[:, 2 * H * dim + H * vdim:2 * H * dim + 2 * H * vdim]
+            ig = cap * np.tanh((p[:, N - 2 * H:N - H] + bias[:H]) / cap)
+            fg = -np.logaddexp(0.0, -cap * np.tanh((p[:, N - H:] + bias[H:]) / cap))
+            want = np.zeros((T, H, vdim))
+            for h in range(H):
+                S, n, m = np.zeros((dim, vdim)), np.zeros(dim), 0.0
+                for t in range(T):
+                    m_new = max(fg[t, h] + m, ig[t, h])
+                    a, b = np.exp(fg[t, h] + m - m_new), np.exp(ig[t, h] - m_new)
+                    S, n, m = a * S + b * np.outer(k[t, h], v[t, h]), a * n + b * k[t, h], m_new
+                    want[t, h] = S.T @ q[t, h] / (max(abs(n @ q[t, h]), np.exp(-m)) + 1e-6)
+            want = PM.rms(want, 1e-5).reshape(T, H * vdim) * nw * PM.sigmoid(gate)
+            assert np.abs(np.concatenate(outs[i]) - want).max() < 3e-5 * max(1.0, np.abs(want).max()), (H, dim, vdim, i)
+            # the slot holds the state after the last token, m included
+            st = state[slots[i]].cpu().numpy()
+            assert np.allclose(st[H * dim * vdim + H * dim + h], m, rtol=1e-5, atol=1e-5)
+            assert np.allclose(st[h * dim * vdim:(h + 1) * dim * vdim].reshape(dim, vdim), S, rtol=1e-4, atol=1e-5)
+            assert np.allclose(st[H * dim * vdim + h * dim:H * dim * vdim + (h + 1) * dim], n, rtol=1e-4, atol=1e-5)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_the_routed_feed_forward_kernels(dtype):
+    """Choice and weights against a sort; equal logits go to the lower index; every expert's product against NumPy; the result is
+    ADDED to what the row held."""
+    from vitna_anchor_b200 import ops
+    rng = np.random.default_rng(6)
+    for (T, W, E, top, ff) in ((9, 32, 5, 2, 24), (3, 40, 33, 7, 10), (17, 64, 2, 2, 72), (1, 24, 4, 1, 8)):
+        x = _dev(rng.standard_normal((T, W)), dtype)
+        wr, br = rng.standard_normal((E, W)).astype(np.float32), rng.standard_normal(E).astype(np.float32)
+        if E > 2:
+            wr[2], br[2] = wr[1], br[1]                                   # two experts with the same logit for every token
+        ids = torch.empty(T, top, dtype=torch.int32, device="cuda")
+        wts = torch.empty(T, top, dtype=torch.float32, device="cuda")
+        ops.experts_route(x, _dev(wr), _dev(br), top, ids, wts)
+        xf = x.float().cpu().numpy().astype(np.float64)
+        z = (xf @ wr.astype(np.float64).T + br).astype(np.float32)       # the kernel's logits are float32: ties are ties there too
+        z[:, 2:3] = z[:, 1:2] if E > 2 else z[:, 2:3]
+        want_ids = np.argsort(-z, axis=1, kind="stable")[:, :top]
+        got_ids = ids.cpu().numpy()
+        srt = np.sort(-z, axis=1)
+        for t in range(T):
+            if top < E and 0 < srt[t, top] - srt[t, top - 1] < 1e-4:      # a close call that the order of a float32 sum may turn
+                continue
+            assert sorted(got_ids[t]) == sorted(want_ids[t]), (T, E, t)
+        zz = np.take_along_axis(z.astype(np.float64), got_ids.astype(np.int64), axis=1)
+        e = np.exp(zz - zz.max(1, keepdims=True))
+        assert np.allclose(wts.cpu().numpy(), e / e.sum(1, keepdims=True), atol=1e-5)
+        if E > 2:                                                        # of the equal pair, never 2 without 1
+            assert all(1 in row or 2 not in row for row in got_ids.tolist())
+        gu = _dev(rng.standard_normal((E, 2 * ff, W)) * W ** -0.5, dtype)
+        dn = _dev(rng.standard_normal((E, W, ff)) * ff ** -0.5, dtype)
+        y0 = rng.standard_normal((T, W)).astype(np.float32)
+        y = _dev(y0)
+        ops.experts_apply(x, gu, dn, ids, wts, torch.empty(T * top, ff, dtype=dtype, device="cuda"), y, "silu")
+        ops.check_device_errors()
+        guf, dnf, w_ = gu.float().cpu().numpy().astype(np.float64), dn.float().cpu().numpy().astype(np.float64), wts.cpu().numpy()
+        want = y0.astype(np.float64)
+        for t in range(T):
+            for j in range(top):
+                ex = got_ids[t, j]
+                g, u = guf[ex, :ff] @ xf[t], guf[ex, ff:] @ xf[t]
+                want[t] += w_[t, j] * (dnf[ex] @ (g * PM.sigmoid(g) * u))
+        tol = 2e-5 if dtype == torch.float32 else 3e-2
+        assert np.abs(y.cpu().numpy() - want).max() < tol * max(1.0, np.abs(want).max()), (T, W, E, top, ff)
+
+
+def test_the_output_norm_step_and_the_clamped_activation():
+    from vitna_anchor_b200 import ops
+    rng = np.random.default_rng(7)
+    for (T, W) in ((5, 24), (37, 200), (2, 1000)):
+        x0, y0, w = rng.standard_normal((T, W)), rng.standard_normal((T, W)) * 3, 1 + 0.2 * rng.standard_normal(W)
+        x, y = _dev(x0), _dev(y0)
+        xc = torch.empty(T, W, dtype=torch.bfloat16, device="cuda")
+        ops.residual_norm_step(x, y, _dev(w), xc, 1e-3, 0.4)
+        want = x0 + 0.4 * PM.rms(y0, 1e-3) * w
+        assert np.abs(x.cpu().numpy() - want).max() < 2e-6 * max(1.0, np.abs(want).max())
+        assert float(y.abs().max()) == 0.0                               # left zeroed for the next sublayer
+        assert torch.equal(xc, x.to(torch.bfloat16))
+        y.fill_(1.0)
+        ops.residual_norm_step(x, y, None, xc)                           # the form that starts a pass: nothing is added
+        assert np.abs(x.cpu().numpy() - want).max() < 2e-6 * max(1.0, np.abs(want).max()) and float(y.abs().max()) == 0.0
+    for dtype, tol in ((torch.float32, 2e-6), (torch.bfloat16, 1e-2)):
+        gu = _dev(rng.standard_normal((7, 2 * 45)) * 2, dtype)
+        out = torch.empty(7, 45, dtype=dtype, device="cuda")
+        ops.glu_clamped(gu, out, 1.25, 1.702)
+        g_, u_ = gu.float().cpu().numpy()[:, :45].astype(np.float64), gu.float().cpu().numpy()[:, 45:].astype(np.float64)
+        g_, u_ = np.minimum(g_, 1.25), np.clip(u_, -1.25, 1.25)          # the gate is clamped from above only
+        assert (g_ < -1.25).any()
+        assert np.abs(out.float().cpu().numpy() - g_ * PM.sigmoid(1.702 * g_) * (u_ + 1)).max() < tol * 4
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# the engine's own entry point and scheduler, the command line, the replay program
+# ---------------------------------------------------------------------------------------------------------------
+
+def _plain_greedy(model_dir, ids, n):
+    cfg, W = PM.read_model(model_dir)
+    ids = list(ids)
+    for _ in range(n):
+        ids.append(int(np.argmax(PM.forward(cfg, W, ids)[-1])))
+    return ids[-n:]
+
+
+def test_greedy_generation_through_the_engine_and_its_scheduler(models):
+    from vitna_anchor_b200.engine.engine import Engine
+    d, reqs, _ = models["all"]
+    eng = Engine(d, dtype="float32", parallel=3, kv_block=8, max_batch_tokens=64, max_prompt_portion=24)
+    prompts = [reqs["r2"], reqs["r5"], reqs["r1"], reqs["r3"][:30]]       # four requests through three slots
+    handles = [eng.add_request(p, max_new=12) for p in prompts]
+    while eng.scheduler.has_work():
+        eng.step()
+    eng.flush()
+    for h, p in zip(handles, prompts):
+        assert list(h.output) == _plain_greedy(d, p, 12)
+    assert eng.generate(prompts[0], max_new=12) == _plain_greedy(d, prompts[0], 12)
+
+
+def test_the_replay_program_and_the_command_line(models, tmp_path):
+    d, reqs, ref = models["wide"]
+    rp = RU.Replay(d, "float32", tmp_path / "out", max_tokens=256, kv_block=8)
+    got = rp.run(RU.changing_portions("a", reqs["r4"]) + RU.tail_one_by_one("b", reqs["r2"], tail=10), MM.CONFIGS["wide"]["vocab"])
+    rp.close()
+    assert _worst(got, {"a": ref["r4"], "b": ref["r2"]}, False) < F32_TOL
+    out = subprocess.run([sys.executable, os.path.join(RU.ROOT, "bin", "vitna-anchor"), "generate", "--model", d, "--ids",
+                          ",".join(map(str, reqs["r5"])), "--max-new", "8", "--greedy", "--dtype", "float32"], capture_output=True, text=True)
+    assert out.returncode == 0, out.stderr
+    assert _plain_greedy(d, reqs["r5"], 8) == [int(t) for t in json.loads(out.stdout.strip().splitlines()[-1])["ids"]]
