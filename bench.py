@@ -531,6 +531,12 @@ def kind_of(launch):
         return "attention"
     if launch.startswith(("delta", "cdelta")):
         return "delta"
+    if launch.startswith("mlstm"):
+        return "mlstm"
+    if launch.startswith("experts"):
+        return "experts"
+    if launch in ("embed_hashed", "residual_norm_step", "glu_clamped", "diff_attn_prepare", "diff_attn_combine"):
+        return "between"
     if launch in ("hyper_step", "rmsnorm_rows", "layernorm_rows", "act_mul", "latent_prepare", "latent_rotate_q", "head_gate", "qk_norm_store"):
         return "between"
     return "other"
@@ -672,6 +678,96 @@ def lupanex_run(a, pk, clocks):
         results[name] = row
     return results
 
+# ---------------------------------------------------------------------------------------------------------------
+# --workload manatar
+# ---------------------------------------------------------------------------------------------------------------
+
+# Manatar beside Lupanex (one residual stream), the engine's closest design: both keep a paged cache with grouped heads in one
+# layer of four and a recurrent matrix state in the other three, and both run the same attention and product kernels.  A
+# differential head is two score maps, so Manatar has half Lupanex's heads (equal query and key rows); its gated feed-forward is two
+# thirds as wide as Lupanex's plain one (equal weights).  "moe" replaces every feed-forward by 8 experts of which a token uses 2,
+# each a quarter as wide, plus a shared one half as wide: the weights a token uses are those of the dense form.
+MANATAR_SIZES = {
+    "w1024": dict(width=1024, ff=2816, heads=4, kv=2, dim=64, vdim=128, layers=8, lupanex=dict(heads=8, kv=4, dim=64, vdim=64, ff=4224)),
+    "w2048": dict(width=2048, ff=8192, heads=8, kv=2, dim=128, vdim=128, layers=8, lupanex=dict(heads=16, kv=4, dim=128, vdim=128, ff=12288)),
+}
+MANATAR_EXPERTS, MANATAR_TOP = 8, 2
+
+
+def manatar_config(sz, moe):
+    rot = dict(base=100000.0, dims=sz["dim"] // 2, scaling=dict(factor=4.0, original=1024, fast=24.0, slow=2.0))
+    att = dict(heads=sz["heads"], kv_heads=sz["kv"], dim=sz["dim"], vdim=sz["vdim"], conv=4, diff=0.3, scale=sz["dim"] ** -0.5, rot=rot)
+    mem = dict(heads=sz["heads"], dim=sz["dim"], vdim=2 * sz["vdim"], gate_cap=15.0)
+    mlp = dict(kind="dense", ff=sz["ff"], limit=7.0)
+    if moe:
+        mlp = dict(kind="moe", expert=dict(ff=sz["ff"] // 4), router=dict(experts=MANATAR_EXPERTS, top=MANATAR_TOP), shared=dict(ff=sz["ff"] // 2))
+    layers = [dict(type="attention" if i % 4 == 3 else "mlstm", mixer=att if i % 4 == 3 else mem, mlp=mlp) for i in range(sz["layers"])]
+    return dict(architecture="Manatar", vocab=LUPANEX_VOCAB, width=sz["width"], norm=dict(eps=1e-6), residual_mult=0.5,
+                embedding=dict(bigram=dict(buckets=65536, mul_prev=1000003, mul_cur=31)), layers=layers)
+
+
+def manatar_work(sz, T, moe):
+    """Algorithmic work of one T-token prompt, by kind of kernel: (flops, bytes)."""
+    W, L = sz["width"], sz["layers"]
+    n_att = L // 4
+    n_mem = L - n_att
+    H, G, dk, dv = sz["heads"], sz["kv"], sz["dim"], sz["vdim"]
+    mv = 2 * dv
+    att_rows, mem_rows = 2 * H * dk + 2 * G * dk + G * dv + H * dv, 2 * H * dk + 2 * H * mv + 2 * H
+    ff_w = 3 * W * sz["ff"]
+    if moe:
+        ff_w = 3 * W * (sz["ff"] // 2)                  # the shared one; the routed ones are the experts' kernels
+    w = {
+        "product": (2.0 * T * (n_att * W * (att_rows + H * dv) + n_mem * W * (mem_rows + H * mv) + L * ff_w), 0.0),
+        "attention": (n_att * float(T) * (T + 1) * 2 * H * (dk + dv), 0.0),
+        "mlstm": (n_mem * 5.0 * T * H * dk * mv, n_mem * T * (4.0 * mem_rows + 3 * 4.0 * H * mv + 2.0 * H * mv)),
+        "between": (0.0, (2 * L + 1) * T * W * 18.0 + n_att * T * (4.0 * att_rows + 2.0 * (2 * H * dk + 2 * G * dk + G * dv) + 2.0 * 3 * H * dv)),
+    }
+    if moe:
+        e_ff = sz["ff"] // 4
+        w["experts"] = (L * 2.0 * T * MANATAR_TOP * 3 * W * e_ff, L * MANATAR_EXPERTS * 3.0 * W * e_ff * 2)
+    return w
+
+
+def manatar_lupanex_config(sz):
+    c = lupanex_config(dict(sz, **sz["lupanex"]))
+    del c["streams"]
+    return c
+
+
+def manatar_lupanex_work(sz, T):
+    w = lupanex_work(dict(sz, **sz["lupanex"]), T)
+    w["between"] = (0.0, (2 * sz["layers"] + 1) * T * sz["width"] * 6.0)
+    return w
+
+
+def manatar_run(a, pk, clocks):
+    import torch
+    from vitna_anchor_b200.engine.loading import random_model_on_device
+    results = {}
+    for name, sz in MANATAR_SIZES.items():
+        row = {}
+        for which, cfg, work in (("manatar", manatar_config(sz, False), manatar_work(sz, PREFILL_TOKENS, False)),
+                                 ("manatar_moe", manatar_config(sz, True), manatar_work(sz, PREFILL_TOKENS, True)),
+                                 ("lupanex", manatar_lupanex_config(sz), manatar_lupanex_work(sz, PREFILL_TOKENS))):
+            model = random_model_on_device(cfg, 0)
+            if model.max_positions > CONTEXT:
+                model.max_positions = CONTEXT           # the design has no limit of its own; the run's cache has
+            pf = prefill_run(model, None, clocks, repeats=3)
+            dec = decode_run(model, a.batch, min(a.steps, 32), a.warmup, clocks, with_e2e=False)
+            flops = sum(f for f, _ in work.values())
+            row[which] = {"weights_mb": round(model.step_weight_bytes() / 1e6, 1),
+                          "prefill_2048": {"tokens_per_s": round(pf["value"]), "ms": round(pf["ms"], 3),
+                                           "frac_bf16": round(flops / (pf["ms"] * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)},
+                          f"decode_b{a.batch}": {"tokens_per_s": round(dec["value"]), "ms_per_step": round(dec["ms_per_step"], 4),
+                                                 "frac_hbm": round(dec["gbs"] / pk["hbm_gbs"], 4), "launches_per_step": dec["launches"] // min(a.steps, 32)},
+                          "prompt_by_kind": prompt_by_kind(model, work, pk)}
+            del model
+            torch.cuda.empty_cache()
+        results[name] = row
+    return results
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -680,9 +776,9 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--model", default="135M", choices=sorted(MODELS), help="layer sizes: SmolLM2-135M (the default), 360M or 1.7B")
-    ap.add_argument("--workload", default="decode", choices=["decode", "mixed", "prefill8k", "lupanex", "siparax"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "mixed", "prefill8k", "lupanex", "siparax", "manatar"],
                     help="decode (the default line), mixed (32 requests, 512-token portions beside decodes), prefill8k, lupanex "
-                         "(the Lupanex design beside a Llama model of equal size)")
+                         "(the Lupanex design beside a Llama model of equal size), siparax and manatar (those designs beside Lupanex)")
     ap.add_argument("--no-points", action="store_true", help="skip the other batches, models and the prefill")
     ap.add_argument("--only-prefill", action="store_true", help="run the prefill measurement alone (for profiling)")
     ap.add_argument("--profile-region", default="", choices=["", "decode", "prefill"],
@@ -725,6 +821,15 @@ def main():
         print(json.dumps({"metric": "Siparax beside Lupanex (one residual stream) at equal width, depth and feed-forward weights: tokens/s of a "
                           f"2,048-token prompt and of batch-{a.batch} decoding from 2,048-token prompts; a prompt's time by kind of kernel "
                           "against its roofline", "impl": "ours", "dtype": "bf16",
+                          "data": "synthetic: random weights drawn on the device, uniform-random token ids", "peaks": pk, "sizes": r,
+                          "clocks": clocks.summary()}))
+        return 0
+    if a.workload == "manatar":
+        r = manatar_run(a, pk, clocks)
+        clocks.stop()
+        print(json.dumps({"metric": "Manatar (dense and routed feed-forwards) beside Lupanex (one residual stream) at equal width, depth and "
+                          f"weights a token uses: tokens/s of a 2,048-token prompt and of batch-{a.batch} decoding from 2,048-token prompts; "
+                          "a prompt's time by kind of kernel against its roofline", "impl": "ours", "dtype": "bf16",
                           "data": "synthetic: random weights drawn on the device, uniform-random token ids", "peaks": pk, "sizes": r,
                           "clocks": clocks.summary()}))
         return 0
