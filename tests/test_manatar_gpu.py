@@ -369,7 +369,7 @@ def test_the_matrix_memory_kernel_against_the_recurrence_written_out():
             ctx = SimpleNamespace(seg_starts=_dev(np.concatenate([[0], np.cumsum(lens_p)]), torch.int32), seg_slots=_dev(slots_p, torch.int32),
                                   num_segments=len(lens_p))
             out = torch.empty(T, H * vdim, device="cuda")
-            ops.mlstm(_dev(rows), _dev(bias), cap, _dev(nw), 1e-5, ctx, state, torch.empty(T, H * vdim, device="cuda"), out, H, dim, vdim)
+            ops.mlstm(_dev(rows), _dev(bias), cap, _dev(nw), 1e-5, ctx, state, torch.empty(T, H * (vdim + 2), device="cuda"), out, H, dim, vdim)
             o = out.cpu().numpy()
             at = 0
             for i, n in enumerate(lens):

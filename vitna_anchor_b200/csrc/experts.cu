@@ -7,6 +7,14 @@
 //  experts_down      y[token] += sum_k weight_k W_down,e_k act[token, k], the experts of a token summed in the order of its list, so
 //                    that the sum does not depend on what else is in the batch.
 //
+// For a prompt's portion in bfloat16 the experts' products run on the tensor cores as products of row groups (linear_tcgen05.cu):
+//  experts_sort      one block: counts the copies a group (an expert) gets, gives every group whole tiles of 128 rows one after another,
+//                    and writes for each (token, k) its row, for each row its token (-1: a fill row), for each tile its group
+//                    (-1: unused).  Which copy of a group gets which of its rows is left to the order of arrival: a row's product
+//                    does not depend on where in a tile it stands.
+//  experts_gather    a block a row: the token's input row is copied to its row of the grouped matrix.
+//  experts_combine   a block a token: y[token] += sum_k weight_k out[row of (token, k)], in the order of the token's list.
+//
 // Nothing here comes to the host: which experts run is read by the kernels from the ids on the device, so a captured graph
 // replays the part for any batch.  Products accumulate in float32 (fmaf); storage is float32 or bfloat16.
 #include "common.cuh"
@@ -117,9 +125,116 @@ __global__ void __launch_bounds__(256) experts_down_kernel(const T* __restrict__
     }
 }
 
+constexpr int EXPERT_TILE = 128;                        // rows of a tile of the grouped products
+
+__global__ void __launch_bounds__(1024) experts_sort_kernel(const int32_t* __restrict__ ids, int n, int E, int rows_max, int32_t* __restrict__ pos,
+                                                            int32_t* __restrict__ row_token, int32_t* __restrict__ tile_group, int top) {
+    extern __shared__ int sort_sh[];                    // count [E] | start [E]
+    int* count = sort_sh;
+    int* start = sort_sh + E;
+    dependency_wait();
+    let_dependents_start();
+    for (int e = threadIdx.x; e < E; e += blockDim.x) count[e] = 0;
+    for (int i = threadIdx.x; i < rows_max; i += blockDim.x) row_token[i] = -1;
+    for (int i = threadIdx.x; i < rows_max / EXPERT_TILE; i += blockDim.x) tile_group[i] = -1;
+    __syncthreads();
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const int e = ids[i];
+        if (e >= 0 && e < E) atomicAdd(&count[e], 1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int at = 0;
+        for (int e = 0; e < E; e++) {
+            start[e] = at;
+            at += (count[e] + EXPERT_TILE - 1) / EXPERT_TILE * EXPERT_TILE;
+        }
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+        for (int r = start[e]; r < start[e] + count[e] && r < rows_max; r += EXPERT_TILE) tile_group[r / EXPERT_TILE] = e;
+        count[e] = 0;                                   // from here on: the rows of the group that are taken
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const int e = ids[i];
+        int r = -1;
+        if (e >= 0 && e < E) {
+            r = start[e] + atomicAdd(&count[e], 1);
+            if (r < rows_max) row_token[r] = i / top; else r = -1;
+        }
+        pos[i] = r;
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(128) experts_gather_kernel(const T* __restrict__ x, int width, const int32_t* __restrict__ row_token,
+                                                             T* __restrict__ xs) {
+    dependency_wait();
+    let_dependents_start();
+    const int t = row_token[blockIdx.x];
+    if (t < 0) return;
+    const T* src = x + (size_t)t * width;
+    T* dst = xs + (size_t)blockIdx.x * width;
+    constexpr int V = Vec16<T>::N;
+    if (width % V == 0 && ((uintptr_t)x % 16 == 0) && ((uintptr_t)xs % 16 == 0)) {
+        for (int i = threadIdx.x; i < width / V; i += blockDim.x) reinterpret_cast<uint4*>(dst)[i] = reinterpret_cast<const uint4*>(src)[i];
+    } else {
+        for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = src[i];
+    }
+}
+
+__global__ void __launch_bounds__(256) experts_combine_kernel(const float* __restrict__ o, int width, int top, const int32_t* __restrict__ pos,
+                                                              const float* __restrict__ wts, float* __restrict__ y) {
+    dependency_wait();
+    let_dependents_start();
+    const int t = blockIdx.x;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        float total = 0.0f;
+        for (int k = 0; k < top; k++) {
+            const int r = pos[(size_t)t * top + k];
+            if (r >= 0) total = fmaf(wts[(size_t)t * top + k], o[(size_t)r * width + c], total);
+        }
+        y[(size_t)t * width + c] += total;
+    }
+}
+
 }  // namespace vk
 
 using namespace vk;
+
+// Rows that the grouped matrix needs for `tokens` tokens at most: every copy, and every group filled up to a whole tile.
+VK_API int vk_experts_grouped_rows(int tokens, int top, int E) {
+    const long long rows = ((long long)tokens * top + (long long)E * (EXPERT_TILE - 1) + EXPERT_TILE - 1) / EXPERT_TILE * EXPERT_TILE;
+    return rows > 0x7fffffffLL ? -1 : (int)rows;
+}
+
+// ids int32 [tokens][top] -> pos int32 [tokens][top], row_token int32 [rows_max], tile_group int32 [rows_max / 128];
+// rows_max = vk_experts_grouped_rows(tokens, top, E).
+VK_API int vk_experts_sort(const int32_t* ids, int tokens, int top, int E, int rows_max, int32_t* pos, int32_t* row_token, int32_t* tile_group,
+                           cudaStream_t stream) {
+    if (tokens <= 0) return VK_OK;
+    if (top <= 0 || E <= 0 || rows_max < vk_experts_grouped_rows(tokens, top, E) || rows_max % EXPERT_TILE) return VK_BAD_SHAPE;
+    const size_t smem = 2 * (size_t)E * sizeof(int);
+    if (smem > 48 * 1024) return VK_TOO_LARGE;
+    return launch_dependent(experts_sort_kernel, dim3(1), dim3(1024), smem, stream, ids, tokens * top, E, rows_max, pos, row_token, tile_group, top);
+}
+
+// xs [rows][width] in dtype <- x [tokens][width] by row_token.
+VK_API int vk_experts_gather(const void* x, int width, const int32_t* row_token, void* xs, int rows, int dtype, cudaStream_t stream) {
+    if (rows <= 0) return VK_OK;
+    if (width <= 0) return VK_BAD_SHAPE;
+    if (dtype == 0) return launch_dependent(experts_gather_kernel<float>, dim3(rows), dim3(128), 0, stream, (const float*)x, width, row_token, (float*)xs);
+    return launch_dependent(experts_gather_kernel<__nv_bfloat16>, dim3(rows), dim3(128), 0, stream, (const __nv_bfloat16*)x, width, row_token,
+                            (__nv_bfloat16*)xs);
+}
+
+// y float32 [tokens][width] += sum_k wts[t][k] o[pos[t][k]]; o float32 [rows][width].
+VK_API int vk_experts_combine(const float* o, int width, int top, const int32_t* pos, const float* wts, float* y, int tokens, cudaStream_t stream) {
+    if (tokens <= 0) return VK_OK;
+    if (width <= 0 || top <= 0) return VK_BAD_SHAPE;
+    return launch_dependent(experts_combine_kernel, dim3(tokens), dim3(256), 0, stream, o, width, top, pos, wts, y);
+}
 
 // x [tokens][width] in dtype; wr float32 [E][width], br float32 [E] or null; ids int32 [tokens][top], wts float32 [tokens][top].
 VK_API int vk_experts_route(const void* x, int width, const float* wr, const float* br, int E, int top, int32_t* ids, float* wts, int tokens,

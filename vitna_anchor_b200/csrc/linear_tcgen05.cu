@@ -48,6 +48,11 @@ struct TcExtra {
     __nv_bfloat16* cache;
     int nh, nkv, hd, page_size;
     int act;                     // TC_SAME: an activation on the float32 sums before they are rounded (activate_rt; 0 none)
+    // Products of groups of rows with a weight matrix each (a routed feed-forward's experts): the weight is group_rows rows a group,
+    // one group after another, and row tile number i of x belongs to group tile_group[i] (negative: the tile has no rows and its
+    // blocks leave at once).  The table is the output of a kernel before this one.  Null: one weight matrix for all rows.
+    const int32_t* tile_group;
+    int group_rows;
 };
 
 template <int BN, int EPI>
@@ -69,6 +74,13 @@ __global__ void __launch_bounds__(TC_THREADS) linear_tcgen05_kernel(const __grid
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int m0 = blockIdx.y * TC_BM, n0 = blockIdx.x * (EPI == TC_SWIGLU ? BN / 2 : BN);     // first output column of the tile
     const int num_kb = (K + TC_BK - 1) / TC_BK;
+    int w_row0 = 0;                       // the tile's group's first row of the weight
+    if (ex.tile_group) {
+        dependency_wait();                // the table is written by the kernel before this one
+        const int g = ex.tile_group[blockIdx.y];
+        if (g < 0) return;                // (the whole block: nothing is set up yet)
+        w_row0 = g * ex.group_rows;
+    }
 
     if (threadIdx.x == 0) {
         failed = 0;
@@ -93,10 +105,10 @@ __global__ void __launch_bounds__(TC_THREADS) linear_tcgen05_kernel(const __grid
             // the activation tiles follow the wait.
             auto load_w = [&](int kb, int s) {
                 if (EPI == TC_SWIGLU) {     // rows n0 .. n0+BN/2 of gate, then the same rows of up: the map's box is BN/2 rows
-                    tma_load_2d(smem + s * STAGE_BYTES + A_BYTES, &map_w, kb * TC_BK, n0, &full[s]);
-                    tma_load_2d(smem + s * STAGE_BYTES + A_BYTES + B_BYTES / 2, &map_w, kb * TC_BK, ex.inter + n0, &full[s]);
+                    tma_load_2d(smem + s * STAGE_BYTES + A_BYTES, &map_w, kb * TC_BK, w_row0 + n0, &full[s]);
+                    tma_load_2d(smem + s * STAGE_BYTES + A_BYTES + B_BYTES / 2, &map_w, kb * TC_BK, w_row0 + ex.inter + n0, &full[s]);
                 } else {
-                    tma_load_2d(smem + s * STAGE_BYTES + A_BYTES, &map_w, kb * TC_BK, n0, &full[s]);
+                    tma_load_2d(smem + s * STAGE_BYTES + A_BYTES, &map_w, kb * TC_BK, w_row0 + n0, &full[s]);
                 }
             };
             // (a stage named by wc.skip_stage is left unarmed and unfilled: a test of the give-up path)
@@ -840,6 +852,38 @@ static int linear_tcgen05_gated_impl(const void* x, const void* w, void* out, in
     }
     if (!make_map(&mx, x, M, K, ldx, TC_BM) || !make_map(&mw, w, 2 * inter, K, K, 64)) return VK_BAD_SHAPE;
     return launch_tc<128, TC_SWIGLU>(mx, mw, out, M, 2 * inter, K, error, stream, ex);
+}
+
+// Products of row groups with a weight matrix each.  x [M, K] bfloat16 holds the groups' rows one group after another, every group
+// filled up to whole tiles of 128 rows; tile_group int32 [ceil(M / 128)] on the device names each tile's group (negative: an unused
+// tile).  gated 0: w [groups][N][K], out [M, N] (mode 0 bfloat16, 1 float32) = x w_g^T.  gated 1: w [groups][2 N][K] (a group's gate
+// rows, then its up rows), out [M, N] bfloat16 = f(x gate_g^T) * (x up_g^T), f = silu (act 0) or activate_rt's number act.
+VK_API int vk_linear_tcgen05_grouped(const void* x, const void* w, void* out, int M, int N, int K, int ldx, int groups, const int32_t* tile_group,
+                                     int mode, int gated, int act, int* error, cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return VK_OK;
+    if (K <= 0 || ldx < K || !error || !tile_group || groups <= 0 || K % 8 != 0 || ldx % 8 != 0 || act < 0 || act > 3) return VK_BAD_SHAPE;
+    if (gated ? (N % 8 != 0 || mode != 0) : (mode < 0 || mode > 1 || act != 0)) return VK_BAD_SHAPE;
+    if (((uintptr_t)x % 16) || ((uintptr_t)w % 16) || ((uintptr_t)out % 16)) return VK_BAD_ALIGNMENT;
+    if ((M + TC_BM - 1) / TC_BM > 65535 || (long long)groups * (gated ? 2 : 1) * N > 0x7fffffffLL) return VK_TOO_LARGE;
+    CUtensorMap mx, mw;
+    TcExtra ex{};
+    ex.tile_group = tile_group;
+    ex.act = act;
+    if (gated) {
+        ex.inter = N;
+        ex.group_rows = 2 * N;
+        if (!make_map(&mx, x, M, K, ldx, TC_BM) || !make_map(&mw, w, groups * 2 * N, K, K, 64)) return VK_BAD_SHAPE;
+        return launch_tc<128, TC_SWIGLU>(mx, mw, out, M, 2 * N, K, error, stream, ex);
+    }
+    ex.group_rows = N;
+    const int bn = N >= 2048 ? 128 : 64;
+    if (!make_map(&mx, x, M, K, ldx, TC_BM) || !make_map(&mw, w, groups * N, K, K, bn)) return VK_BAD_SHAPE;
+    if (bn == 128) {
+        if (mode == 0) return launch_tc<128, TC_SAME>(mx, mw, out, M, N, K, error, stream, ex);
+        return launch_tc<128, TC_F32>(mx, mw, out, M, N, K, error, stream, ex);
+    }
+    if (mode == 0) return launch_tc<64, TC_SAME>(mx, mw, out, M, N, K, error, stream, ex);
+    return launch_tc<64, TC_F32>(mx, mw, out, M, N, K, error, stream, ex);
 }
 
 // x [M, K] bfloat16, w [(nh + 2*nkv) * hd, K] bfloat16 (q heads, k heads, v heads); q_out [M, nh*hd] bfloat16 gets the

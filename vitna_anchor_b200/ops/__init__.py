@@ -1335,17 +1335,18 @@ def mlstm_max_dim() -> int:
 def mlstm(proj: torch.Tensor, gate_bias: torch.Tensor, cap: float, norm_w: torch.Tensor, eps: float, ctx, state: torch.Tensor,
           o: torch.Tensor, out: torch.Tensor, H: int, dim: int, vdim: int) -> torch.Tensor:
     """proj float32 [T, N] = q | k | v | gate | a | b; the recurrence token after token per segment from and into `state`
-    [slots, mlstm_state_floats]; out [T, H * vdim] = o / rms(o) * norm_w * sigmoid(gate) in out's dtype."""
+    [slots, mlstm_state_floats]; o float32 [T, H * (vdim + 2)] receives each head's numerators, n . q and m;
+    out [T, H * vdim] = o / rms(o) * norm_w * sigmoid(gate) in out's dtype."""
     _req(proj, "proj", torch.float32, 2); _req(gate_bias, "gate_bias", torch.float32, 1); _req(norm_w, "norm_w", torch.float32, 1)
     _req(state, "state", torch.float32); _req(o, "o", torch.float32, 2); _req(out, "out", dims=2)
     T, N = proj.shape
-    if (N < 2 * H * dim + 2 * H * vdim + 2 * H or gate_bias.shape[0] != 2 * H or norm_w.shape[0] != H * vdim or o.shape != (T, H * vdim)
+    if (N < 2 * H * dim + 2 * H * vdim + 2 * H or gate_bias.shape[0] != 2 * H or norm_w.shape[0] != H * vdim or o.shape != (T, H * (vdim + 2))
             or out.shape != (T, H * vdim) or state[0].numel() != mlstm_state_floats(H, dim, vdim)):
         raise KernelError("mlstm: shapes do not fit the head counts")
     _check(lib().vk_mlstm_recurrence(_p(proj), N, H, dim, vdim, _p(gate_bias), ctypes.c_float(cap), _p(ctx.seg_starts), _p(ctx.seg_slots),
                                      _p(state), _p(o), ctx.num_segments, _stream()), "mlstm_recurrence")
-    _check(lib().vk_mlstm_gate(_p(o), _p(proj), N, 2 * H * dim + H * vdim, _p(norm_w), ctypes.c_float(eps), H, vdim, _p(out), T, _dt(out),
-                               _stream()), "mlstm_gate")
+    _check(lib().vk_mlstm_gate(_p(o), _p(proj), N, 2 * H * dim + H * vdim, _p(norm_w), ctypes.c_float(eps), H, dim, vdim, _p(out), T,
+                               _p(ctx.seg_starts), _p(ctx.seg_slots), _p(state), ctx.num_segments, _dt(out), _stream()), "mlstm_gate")
     return out
 
 

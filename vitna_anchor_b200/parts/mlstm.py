@@ -51,6 +51,6 @@ class MatrixLSTM(Mixer):
             raise ValueError("a recurrent mixer has no cache that another run could read")
         T, ws, HV = ctx.num_tokens, ctx.workspace, self.H * self.vdim
         proj = ops.linear(xn, self.w_in, ws.rows("mlstm.proj", T, self.w_in.shape[0], torch.float32), ops.LINEAR_F32)
-        out = ops.mlstm(proj, self.gate_bias, self.cap, self.norm_weight, self.eps, ctx, cache.state, ws.rows("mlstm.o", T, HV, torch.float32),
+        out = ops.mlstm(proj, self.gate_bias, self.cap, self.norm_weight, self.eps, ctx, cache.state, ws.rows("mlstm.o", T, self.H * (self.vdim + 2), torch.float32),
                         ws.rows("mlstm.out", T, HV, ctx.dtype), self.H, self.dim, self.vdim)
         ops.linear(out, self.w_out, residual, ops.LINEAR_ACC_F32)
