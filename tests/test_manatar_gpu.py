@@ -446,6 +446,51 @@ def test_the_routed_feed_forward_kernels(dtype):
         assert np.abs(y.cpu().numpy() - want).max() < tol * max(1.0, np.abs(want).max()), (T, W, E, top, ff)
 
 
+def test_the_routed_feed_forward_as_products_of_row_groups():
+    """The tensor-core form: copies sorted expert by expert into whole tiles of 128 rows.  Experts that nobody chose, an expert with
+    exactly 128 copies, one with 129, sizes that are no multiple of a tile's columns; against NumPy on the same choice."""
+    from vitna_anchor_b200 import ops
+    rng = np.random.default_rng(16)
+    for (T, W, E, top, ff) in ((300, 64, 6, 2, 72), (257, 136, 5, 3, 200), (128, 64, 3, 1, 64)):
+        x = _dev(rng.standard_normal((T, W)), torch.bfloat16)
+        ids_np = np.stack([rng.permutation(E - 1)[:top] for _ in range(T)]).astype(np.int32)      # the last expert is never chosen
+        if top == 1:
+            ids_np[:, 0] = 0                                             # one expert has every row: a full tile and no more
+        else:
+            ids_np[:, 0], ids_np[:, 1] = 0, 1 + np.arange(T) % (E - 2)
+            ids_np[129:, 0] = ids_np[129:, 1]
+            ids_np[129:, 1] = (ids_np[129:, 0] % (E - 2)) + 1             # expert 0 has 129 copies
+            if top == 3:
+                ids_np[:, 2] = [next(e for e in range(1, E) if e not in row[:2]) for row in ids_np]
+        w_np = rng.random((T, top)).astype(np.float32)
+        ids, wts = _dev(ids_np, torch.int32), _dev(w_np)
+        gu = _dev(rng.standard_normal((E, 2 * ff, W)) * W ** -0.5, torch.bfloat16)
+        dn = _dev(rng.standard_normal((E, W, ff)) * ff ** -0.5, torch.bfloat16)
+        y0 = rng.standard_normal((T, W)).astype(np.float32)
+        y = _dev(y0)
+        rows = ops.experts_grouped_rows(T, top, E)
+        i32 = dict(dtype=torch.int32, device="cuda")
+        pos, row_token, tile_group = torch.empty(T, top, **i32), torch.empty(rows, **i32), torch.empty(rows // 128, **i32)
+        xs = torch.full((rows, W), float("nan"), dtype=torch.bfloat16, device="cuda")         # fill rows stay what they were: nobody reads them
+        act = torch.empty(rows, ff, dtype=torch.bfloat16, device="cuda")
+        o = torch.empty(rows, W, dtype=torch.float32, device="cuda")
+        ops.experts_apply_grouped(x, gu, dn, ids, wts, pos, row_token, tile_group, xs, act, o, y)
+        torch.cuda.synchronize()
+        ops.check_device_errors()
+        # every copy has a row of its own inside a tile of its expert
+        pos_np, rt, tg = pos.cpu().numpy(), row_token.cpu().numpy(), tile_group.cpu().numpy()
+        assert len(set(pos_np.ravel().tolist())) == T * top and pos_np.min() >= 0
+        assert (tg[pos_np // 128] == ids_np).all() and (rt[pos_np] == np.arange(T)[:, None]).all() and (rt >= 0).sum() == T * top
+        xf, guf, dnf = (a.float().cpu().numpy().astype(np.float64) for a in (x, gu, dn))
+        want = y0.astype(np.float64)
+        for t in range(T):
+            for j in range(top):
+                ex = ids_np[t, j]
+                g, u = guf[ex, :ff] @ xf[t], guf[ex, ff:] @ xf[t]
+                want[t] += w_np[t, j] * (dnf[ex] @ (g * PM.sigmoid(g) * u))
+        assert np.abs(y.cpu().numpy() - want).max() < 3e-2 * max(1.0, np.abs(want).max()), (T, W, E, top, ff)
+
+
 def test_the_output_norm_step_and_the_clamped_activation():
     from vitna_anchor_b200 import ops
     rng = np.random.default_rng(7)

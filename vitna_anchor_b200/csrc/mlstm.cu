@@ -148,6 +148,7 @@ __global__ void __launch_bounds__(ML_THREADS) mlstm_recurrence_kernel(const floa
             if (blockIdx.x == 0) o[((size_t)(t0 + tid) * H + h) * OW + vdim + 1] = smn[tid];
         }
         __syncthreads();
+#pragma unroll 4
         for (int t = 0; t < cnt; t++) {
             const float a = sa[t], bv = sb[t] * sv[t * ML_COLS + cl];
             const float4* k4 = reinterpret_cast<const float4*>(sk + t * DP) + rg;

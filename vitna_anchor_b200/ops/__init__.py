@@ -1386,3 +1386,48 @@ def experts_apply(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor
            "experts_gate_up")
     _check(lib().vk_experts_down(_p(act_buf), ff, _p(w_down), W, top, _p(ids), _p(wts), _p(y), T, _dt(x), _stream()), "experts_down")
     return y
+
+
+def experts_grouped_rows(tokens: int, top: int, E: int) -> int:
+    """Rows of the grouped matrix for up to `tokens` tokens: every copy, and every expert's rows filled up to whole tiles."""
+    rows = int(lib().vk_experts_grouped_rows(tokens, top, E))
+    if rows < 0:
+        raise KernelError("experts_grouped_rows: too many rows")
+    return rows
+
+
+def experts_grouped_takes(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor) -> bool:
+    """Whether the tensor-core form takes these operands: bfloat16, 16-byte aligned, sizes that are multiples of 8."""
+    ff, W = w_gate_up.shape[1] // 2, x.shape[1]
+    return (x.dtype == torch.bfloat16 and w_gate_up.dtype == torch.bfloat16 and w_down.dtype == torch.bfloat16 and W % 8 == 0 and ff % 8 == 0
+            and x.stride(0) == W and x.data_ptr() % 16 == 0 and w_gate_up.data_ptr() % 16 == 0 and w_down.data_ptr() % 16 == 0)
+
+
+def experts_apply_grouped(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, pos: torch.Tensor,
+                          row_token: torch.Tensor, tile_group: torch.Tensor, xs: torch.Tensor, act_buf: torch.Tensor, o: torch.Tensor,
+                          y: torch.Tensor, activation: str = "silu") -> torch.Tensor:
+    """experts_apply on the tensor cores: the tokens' copies are put expert by expert into xs [rows, W] (rows =
+    experts_grouped_rows(T, top, E); pos [T, top], row_token [rows], tile_group [rows / 128] int32), two products of row groups give
+    act_buf [rows, ff] (bfloat16) and o [rows, W] (float32), and y [T, W] (float32) += the weighted rows of each token."""
+    _req(x, "x", torch.bfloat16, 2); _req(y, "y", torch.float32, 2); _req(o, "o", torch.float32, 2); _req(xs, "xs", torch.bfloat16, 2)
+    _req(act_buf, "act_buf", torch.bfloat16, 2); _req(pos, "pos", torch.int32, 2); _req(row_token, "row_token", torch.int32, 1)
+    _req(tile_group, "tile_group", torch.int32, 1)
+    T, W = x.shape
+    E, two_ff, _ = w_gate_up.shape
+    ff, top = two_ff // 2, ids.shape[1]
+    rows = experts_grouped_rows(T, top, E)
+    if (not experts_grouped_takes(x, w_gate_up, w_down) or w_gate_up.shape != (E, 2 * ff, W) or w_down.shape != (E, W, ff) or y.shape != (T, W)
+            or xs.shape != (rows, W) or act_buf.shape != (rows, ff) or o.shape != (rows, W) or pos.shape != (T, top) or row_token.shape != (rows,)
+            or tile_group.shape != (rows // 128,)):
+        raise KernelError("experts_apply_grouped: shapes do not fit")
+    if activation not in _EPILOGUE_ACT:
+        raise KernelError(f"experts_apply_grouped: {activation!r} is not one of {sorted(_EPILOGUE_ACT)}")
+    act = 0 if activation == "silu" else _EPILOGUE_ACT[activation]
+    _check(lib().vk_experts_sort(_p(ids), T, top, E, rows, _p(pos), _p(row_token), _p(tile_group), _stream()), "experts_sort")
+    _check(lib().vk_experts_gather(_p(x), W, _p(row_token), _p(xs), rows, _dt(x), _stream()), "experts_gather")
+    _check(lib().vk_linear_tcgen05_grouped(_p(xs), _p(w_gate_up), _p(act_buf), rows, ff, W, W, E, _p(tile_group), 0, 1, act, _p(error_word()),
+                                           _stream()), "linear_tcgen05_grouped")
+    _check(lib().vk_linear_tcgen05_grouped(_p(act_buf), _p(w_down), _p(o), rows, W, ff, ff, E, _p(tile_group), 1, 0, 0, _p(error_word()),
+                                           _stream()), "linear_tcgen05_grouped")
+    _check(lib().vk_experts_combine(_p(o), W, top, _p(pos), _p(wts), _p(y), T, _stream()), "experts_combine")
+    return y

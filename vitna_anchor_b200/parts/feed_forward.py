@@ -100,7 +100,11 @@ class RoutedExperts(FeedForward):
     """w_router float32 [E, hidden] (+ b_router [E]); w_gate_up [E, 2 ff, hidden] (an expert's gate rows, then its up rows) and
     w_down [E, hidden, ff] in the compute dtype; `shared`: a FeedForward every token passes as well (or None).  The router's
     logits are float32 sums over the (compute dtype) input.  Which experts run never comes to the host: the kernels read the
-    choice on the device, so the part is replayed faithfully from a graph."""
+    choice on the device, so the part is replayed faithfully from a graph.  Steps with at least GROUPED_FROM (token, expert) pairs in
+    bfloat16 run the experts as products of row groups on the tensor cores; shorter steps and float32 read each token's experts' rows
+    directly."""
+
+    GROUPED_FROM = 256
 
     def __init__(self, hidden: int, intermediate: int, experts: int, top: int, w_router: torch.Tensor, b_router: Optional[torch.Tensor],
                  w_gate_up: torch.Tensor, w_down: torch.Tensor, shared: Optional[FeedForward] = None, activation: str = "silu"):
@@ -130,8 +134,19 @@ class RoutedExperts(FeedForward):
         ids = ws.rows("moe.ids", T, self.top, torch.int32)
         wts = ws.rows("moe.wts", T, self.top, torch.float32)
         ops.experts_route(xn, self.w_router, self.b_router, self.top, ids, wts)
-        act = ws.flat(f"moe.act/{self.top}/{self.intermediate}", ws.max_tokens * self.top * self.intermediate, ctx.dtype)
-        ops.experts_apply(xn, self.w_gate_up, self.w_down, ids, wts, act[:T * self.top * self.intermediate].view(T * self.top, self.intermediate),
-                          residual, self.activation)
+        if T * self.top >= self.GROUPED_FROM and ops.experts_grouped_takes(xn, self.w_gate_up, self.w_down):
+            # a prompt's portion in bfloat16: the copies sorted expert by expert, two products of row groups on the tensor cores
+            rows, rows_max = ops.experts_grouped_rows(T, self.top, self.E), ops.experts_grouped_rows(ws.max_tokens, self.top, self.E)
+            key = f"{self.top}/{self.E}"
+            xs = ws.flat(f"moe.xs/{key}/{self.hidden}", rows_max * self.hidden, ctx.dtype)[:rows * self.hidden].view(rows, self.hidden)
+            act = ws.flat(f"moe.gact/{key}/{self.intermediate}", rows_max * self.intermediate, ctx.dtype)[:rows * self.intermediate].view(rows, self.intermediate)
+            o = ws.flat(f"moe.o/{key}/{self.hidden}", rows_max * self.hidden, torch.float32)[:rows * self.hidden].view(rows, self.hidden)
+            ops.experts_apply_grouped(xn, self.w_gate_up, self.w_down, ids, wts, ws.rows("moe.pos", T, self.top, torch.int32),
+                                      ws.flat(f"moe.row_token/{key}", rows_max, torch.int32)[:rows],
+                                      ws.flat(f"moe.tile_group/{key}", rows_max // 128, torch.int32)[:rows // 128], xs, act, o, residual, self.activation)
+        else:
+            act = ws.flat(f"moe.act/{self.top}/{self.intermediate}", ws.max_tokens * self.top * self.intermediate, ctx.dtype)
+            ops.experts_apply(xn, self.w_gate_up, self.w_down, ids, wts, act[:T * self.top * self.intermediate].view(T * self.top, self.intermediate),
+                              residual, self.activation)
         if self.shared is not None:
             self.shared.forward(xn, ctx, residual)
