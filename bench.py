@@ -525,6 +525,8 @@ def llama_work(c, T):
 
 
 def kind_of(launch):
+    if launch.startswith("experts") or launch == "linear_tcgen05_grouped":
+        return "experts"
     if launch.startswith("linear"):
         return "product"
     if launch.startswith("attention"):
@@ -533,8 +535,6 @@ def kind_of(launch):
         return "delta"
     if launch.startswith("mlstm"):
         return "mlstm"
-    if launch.startswith("experts"):
-        return "experts"
     if launch in ("embed_hashed", "residual_norm_step", "glu_clamped", "diff_attn_prepare", "diff_attn_combine"):
         return "between"
     if launch in ("hyper_step", "rmsnorm_rows", "layernorm_rows", "act_mul", "latent_prepare", "latent_rotate_q", "head_gate", "qk_norm_store"):
