@@ -6,11 +6,12 @@
 //  S_t = e^(f_t + m_(t-1) - m_t) S_(t-1) + e^(i_t - m_t) k_t v_t^T;   n_t likewise with k_t alone
 //  o_t = S_t^T q_t / (max(|n_t . q_t|, e^(-m_t)) + 1e-6),  q_t scaled by dim^-1/2
 //
-//  mlstm_recurrence   token after token, one block per (32 columns, head, segment).  The columns of a head are those of S and, as
+//  mlstm_recurrence   token after token, one block per (16 columns, head, segment).  The columns of a head are those of S and, as
 //                     column number vdim, n itself (n is the column that a value of 1 would fill), so that nobody works n out twice.
-//                     A warp holds 8 columns; its lanes are 4 groups of rows (group g has rows 16 j + 4 g .. + 3), so a thread keeps
-//                     dim / 4 values of its column in registers, reads keys and queries as float4 and a token's sum over the rows
-//                     ends with two shuffles.  Tokens come in chunks of 32 (16 for keys of more than 128 values) through a ring of
+//                     A warp holds 4 columns; its lanes are 8 groups of rows (group g has rows 32 j + 4 g .. + 3), so a thread keeps
+//                     dim / 8 values of its column in registers, reads keys and queries as float4 and a token's sum over the rows
+//                     ends with three shuffles (a head of 256 values is 17 blocks: the chain is latency, and narrow blocks put it
+//                     on more multiprocessors).  Tokens come in chunks of 32 (16 for keys of more than 128 values) through a ring of
 //                     two stages in shared memory that cp.async fills a chunk ahead: q, k, the block's columns of v and the two
 //                     gates' sums.  For a chunk the gates are worked out side by side (tanh, log sigmoid), one thread carries m
 //                     through the chunk (an addition and a maximum a token), and the factors e^(f + m' - m) and e^(i - m) side by
@@ -31,7 +32,8 @@ namespace vk {
 __device__ __forceinline__ float log_sigmoid(float z) { return fminf(z, 0.0f) - log1pf(expf(-fabsf(z))); }
 
 constexpr int ML_THREADS = 128;
-constexpr int ML_COLS = 32;
+constexpr int ML_COLS = 16;
+constexpr int ML_ROW_GROUPS = 8;
 
 __device__ __forceinline__ void ml_cp4(float* dst, const float* src) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
@@ -40,15 +42,15 @@ __device__ __forceinline__ void ml_cp16(float* dst, const float* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
 }
 
-// Floats of one stage: q [C][4 DPT] | k [C][4 DPT] | v [C][32] | the gates' sums [C][2]
-__host__ __device__ constexpr int ml_stage_floats(int C, int DPT) { return C * (8 * DPT + ML_COLS + 2); }
+// Floats of one stage: q [C][8 DPT] | k [C][8 DPT] | v [C][16] | the gates' sums [C][2]
+__host__ __device__ constexpr int ml_stage_floats(int C, int DPT) { return C * (2 * ML_ROW_GROUPS * DPT + ML_COLS + 2); }
 
 template <int DPT, int C>
 __global__ void __launch_bounds__(ML_THREADS) mlstm_recurrence_kernel(const float* __restrict__ proj, int N, int H, int dim, int vdim,
                                                                       const float* __restrict__ gate_bias, float cap, float qscale,
                                                                       const int32_t* __restrict__ seg_starts, const int32_t* __restrict__ seg_slots,
                                                                       float* __restrict__ state, size_t state_floats, float* __restrict__ o, int vec) {
-    constexpr int DP = 4 * DPT;                                     // rows of the state as the registers hold them (dim rounded up)
+    constexpr int DP = ML_ROW_GROUPS * DPT;                                     // rows of the state as the registers hold them (dim rounded up)
     constexpr int STAGE = ml_stage_floats(C, DPT);
     extern __shared__ __align__(16) float ml_smem[];
     __shared__ float sgi[C], sgf[C], smp[C], smn[C], sa[C], sb[C];
@@ -56,8 +58,8 @@ __global__ void __launch_bounds__(ML_THREADS) mlstm_recurrence_kernel(const floa
     let_dependents_start();
     const int seg = blockIdx.z, h = blockIdx.y, tid = threadIdx.x;
     const int lane = tid & 31, warp = tid >> 5;
-    const int rg = lane >> 3;                                       // rows 16 j + 4 rg .. + 3
-    const int cl = warp * 8 + (lane & 7);
+    const int rg = lane >> 2;                                       // rows 32 j + 4 rg .. + 3
+    const int cl = warp * 4 + (lane & 3);
     const int col0 = blockIdx.x * ML_COLS, col = col0 + cl;
     const int first = seg_starts[seg], end = seg_starts[seg + 1], slot = seg_slots[seg];
     if (first >= end) return;
@@ -71,7 +73,7 @@ __global__ void __launch_bounds__(ML_THREADS) mlstm_recurrence_kernel(const floa
     for (int j = 0; j < DPT / 4; j++)
 #pragma unroll
         for (int i = 0; i < 4; i++) {
-            const int d = 16 * j + 4 * rg + i;
+            const int d = 32 * j + 4 * rg + i;
             S[4 * j + i] = (col_st && d < dim) ? col_st[(size_t)d * col_stride] : 0.0f;
         }
     float m = st ? st[(size_t)H * dim * vdim + (size_t)H * dim + h] : 0.0f;       // (thread 0's copy is the one that is carried)
@@ -156,7 +158,7 @@ __global__ void __launch_bounds__(ML_THREADS) mlstm_recurrence_kernel(const floa
             float p0 = 0.0f, p1 = 0.0f, p2 = 0.0f, p3 = 0.0f;
 #pragma unroll
             for (int j = 0; j < DPT / 4; j++) {
-                const float4 kk = k4[4 * j], qq = q4[4 * j];
+                const float4 kk = k4[ML_ROW_GROUPS * j], qq = q4[ML_ROW_GROUPS * j];
                 S[4 * j + 0] = fmaf(kk.x, bv, a * S[4 * j + 0]);
                 S[4 * j + 1] = fmaf(kk.y, bv, a * S[4 * j + 1]);
                 S[4 * j + 2] = fmaf(kk.z, bv, a * S[4 * j + 2]);
@@ -167,6 +169,7 @@ __global__ void __launch_bounds__(ML_THREADS) mlstm_recurrence_kernel(const floa
                 p3 = fmaf(S[4 * j + 3], qq.w, p3);
             }
             float po = (p0 + p1) + (p2 + p3);
+            po += __shfl_xor_sync(0xffffffffu, po, 4);
             po += __shfl_xor_sync(0xffffffffu, po, 8);
             po += __shfl_xor_sync(0xffffffffu, po, 16);
             if (rg == 0 && col <= vdim) o[((size_t)(t0 + t) * H + h) * OW + col] = po * qscale;
@@ -178,7 +181,7 @@ __global__ void __launch_bounds__(ML_THREADS) mlstm_recurrence_kernel(const floa
     for (int j = 0; j < DPT / 4; j++)
 #pragma unroll
         for (int i = 0; i < 4; i++) {
-            const int d = 16 * j + 4 * rg + i;
+            const int d = 32 * j + 4 * rg + i;
             if (d < dim) col_st[(size_t)d * col_stride] = S[4 * j + i];
         }
 }
@@ -223,7 +226,7 @@ using namespace vk;
 VK_API int vk_mlstm_max_dim() { return 256; }
 
 // proj float32 [tokens][N] = q [H dim] | k [H dim] | v [H vdim] | gate [H vdim] | a [H] | b [H];  gate_bias float32 [2H] (a's, then b's);
-// state float32 [slots][H dim vdim + H dim + H];  o float32 [tokens][H][vdim + 2] (numerators, n . q, m).  A block a (32 columns, head,
+// state float32 [slots][H dim vdim + H dim + H];  o float32 [tokens][H][vdim + 2] (numerators, n . q, m).  A block a (16 columns, head,
 // segment): segments is the step's count, whatever their lengths.  S and n of the state are written here, m by vk_mlstm_gate.
 VK_API int vk_mlstm_recurrence(const float* proj, int N, int H, int dim, int vdim, const float* gate_bias, float cap, const int32_t* seg_starts,
                                const int32_t* seg_slots, float* state, float* o, int segments, cudaStream_t stream) {
@@ -244,10 +247,10 @@ VK_API int vk_mlstm_recurrence(const float* proj, int N, int H, int dim, int vdi
         return launch_dependent(kern, grid, dim3(ML_THREADS), smem, stream, proj, N, H, dim, vdim, gate_bias, cap, qscale, seg_starts,       \
                                 seg_slots, state, state_floats, o, vec);                                                                     \
     } while (0)
-    if (dim <= 32) VK_MLSTM(8, 32);
-    if (dim <= 64) VK_MLSTM(16, 32);
-    if (dim <= 128) VK_MLSTM(32, 32);
-    VK_MLSTM(64, 16);
+    if (dim <= 32) VK_MLSTM(4, 32);
+    if (dim <= 64) VK_MLSTM(8, 32);
+    if (dim <= 128) VK_MLSTM(16, 32);
+    VK_MLSTM(32, 16);
 #undef VK_MLSTM
 }
 
