@@ -91,8 +91,8 @@ class ClampedGLU(FeedForward):
 
     def forward(self, xn: torch.Tensor, ctx: StepContext, residual: torch.Tensor, norm=None) -> None:
         T, ws = ctx.num_tokens, ctx.workspace
-        gu = ops.linear(xn, self.w_gate_up, ws.rows("ffn.gu", T, 2 * self.intermediate, ctx.dtype), ops.LINEAR_SAME)
-        act = ops.glu_clamped(gu, ws.rows("ffn.act", T, self.intermediate, ctx.dtype), self.limit, self.alpha)
+        act = ops.linear_glu_clamped(xn, self.w_gate_up, ws.rows("ffn.gu", T, 2 * self.intermediate, ctx.dtype),
+                                     ws.rows("ffn.act", T, self.intermediate, ctx.dtype), self.limit, self.alpha)
         ops.linear(act, self.w_down, residual, ops.LINEAR_ACC_F32)
 
 
