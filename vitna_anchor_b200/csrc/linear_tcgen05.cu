@@ -62,7 +62,9 @@ __device__ __forceinline__ float tc_gated(const TcExtra& ex, float g, float up) 
     if (ex.act == 4) {
         g = fminf(g, ex.limit);
         up = fminf(fmaxf(up, -ex.limit), ex.limit);
-        return (g / (1.0f + expf(-ex.alpha * g))) * (up + 1.0f);
+        float e;                 // 2^x and the reciprocal from the special-function unit, as in tc_silu_mul: the result is rounded to bfloat16
+        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-1.4426950408889634f * ex.alpha * g));
+        return __fdividef(g, 1.0f + e) * (up + 1.0f);
     }
     return ex.act ? activate_rt(ex.act, g) * up : tc_silu_mul(g, up);
 }
