@@ -109,6 +109,7 @@ ALONE = {
     "embedding_pair": MM.config(40, 32, [MM.layer("mlstm", MM.mem(1, 8, 8, 5.0))], bigram=(7, 5, 3)),
     "attention_bare": MM.config(40, 32, [MM.layer("attention", _A(2, 2, 8, 8, 0, 0.3, 0.4, None))], bigram=None),
     "attention_conv": MM.config(40, 32, [MM.layer("attention", _A(2, 1, 16, 8, 4, 0.3, 0.3, None))], bigram=None),
+    "attention_conv_one_tap": MM.config(40, 32, [MM.layer("attention", _A(1, 1, 8, 24, 1, 0.3, 0.5, None))], bigram=None, mult=1.0),
     "attention_rot": MM.config(40, 32, [MM.layer("attention", _A(3, 3, 16, 24, 0, 0.2, 0.3, MM.rot(40.0, 16)))], bigram=None),
     "attention_rot_part": MM.config(40, 32, [MM.layer("attention", _A(4, 2, 32, 16, 2, 0.2, 0.2, MM.rot(1000.0, 12, (8.0, 32, 4.0, 1.0))))]),
     "attention_kv_from": MM.config(40, 32, [MM.layer("attention", _A(2, 1, 16, 16, 3, 0.3, 0.3, MM.ROT_A)),
