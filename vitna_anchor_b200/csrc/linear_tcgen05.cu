@@ -48,26 +48,12 @@ struct TcExtra {
     __nv_bfloat16* cache;
     int nh, nkv, hd, page_size;
     int act;                     // TC_SAME: an activation on the float32 sums before they are rounded (activate_rt; 0 none)
-    float limit, alpha;          // TC_SWIGLU with act 4: min(gate, limit) sigmoid(alpha gate) (clamp(up, -limit, limit) + 1)
     // Products of groups of rows with a weight matrix each (a routed feed-forward's experts): the weight is group_rows rows a group,
     // one group after another, and row tile number i of x belongs to group tile_group[i] (negative: the tile has no rows and its
     // blocks leave at once).  The table is the output of a kernel before this one.  Null: one weight matrix for all rows.
     const int32_t* tile_group;
     int group_rows;
 };
-
-// The gated epilogues' value from the (bfloat16-rounded) gate and up sums: act 0 silu by the special-function unit, 1 to 3
-// activate_rt's functions, 4 the clamped form.
-__device__ __forceinline__ float tc_gated(const TcExtra& ex, float g, float up) {
-    if (ex.act == 4) {
-        g = fminf(g, ex.limit);
-        up = fminf(fmaxf(up, -ex.limit), ex.limit);
-        float e;                 // 2^x and the reciprocal from the special-function unit, as in tc_silu_mul: the result is rounded to bfloat16
-        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-1.4426950408889634f * ex.alpha * g));
-        return __fdividef(g, 1.0f + e) * (up + 1.0f);
-    }
-    return ex.act ? activate_rt(ex.act, g) * up : tc_silu_mul(g, up);
-}
 
 template <int BN, int EPI>
 __global__ void __launch_bounds__(TC_THREADS) linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x,
@@ -215,7 +201,7 @@ __global__ void __launch_bounds__(TC_THREADS) linear_tcgen05_kernel(const __grid
                         for (int e = 0; e < 2; e++) {
                             const float gte = __bfloat162float(__float2bfloat16_rn(__uint_as_float(gr[j + e])));
                             const float up = __bfloat162float(__float2bfloat16_rn(__uint_as_float(ur[j + e])));
-                            a[e] = tc_gated(ex, gte, up);
+                            a[e] = ex.act ? activate_rt(ex.act, gte) * up : tc_silu_mul(gte, up);
                         }
                         __nv_bfloat162 v = __floats2bfloat162_rn(a[0], a[1]);
                         packed[j / 2] = *reinterpret_cast<uint32_t*>(&v);
@@ -548,7 +534,7 @@ __global__ void __launch_bounds__(TW_THREADS, 1) linear_tcgen05_wide_kernel(cons
                                 for (int e = 0; e < 2; e++) {
                                     const float gte = __bfloat162float(__float2bfloat16_rn(__uint_as_float(gr[q + e])));
                                     const float up = __bfloat162float(__float2bfloat16_rn(__uint_as_float(ur[q + e])));
-                                    v[e] = tc_gated(ex, gte, up);
+                                    v[e] = ex.act ? activate_rt(ex.act, gte) * up : tc_silu_mul(gte, up);
                                 }
                                 __nv_bfloat162 pk = __floats2bfloat162_rn(v[0], v[1]);
                                 packed[q / 2] = *reinterpret_cast<uint32_t*>(&pk);
@@ -827,7 +813,7 @@ VK_API int vk_linear_tcgen05_act(const void* x, const void* w, void* out, int M,
 // x [M, K] bfloat16 (row stride ldx), w [2*inter, K] bfloat16 with gate rows then up rows, out [M, inter] bfloat16 =
 // silu(x gate^T) * (x up^T).  inter a multiple of 8.
 static int linear_tcgen05_gated_impl(const void* x, const void* w, void* out, int M, int inter, int K, int ldx, int act, int* error,
-                                     cudaStream_t stream, float limit = 0.0f, float alpha = 0.0f);
+                                     cudaStream_t stream);
 
 VK_API int vk_linear_tcgen05_swiglu(const void* x, const void* w, void* out, int M, int inter, int K, int ldx, int* error,
                                     cudaStream_t stream) {
@@ -841,14 +827,8 @@ VK_API int vk_linear_tcgen05_gated(const void* x, const void* w, void* out, int 
     return linear_tcgen05_gated_impl(x, w, out, M, inter, K, ldx, act, error, stream);
 }
 
-// The clamped gated form: out = g sigmoid(alpha g) (u + 1) with g = min(x gate^T, limit), u = clamp(x up^T, -limit, limit).
-VK_API int vk_linear_tcgen05_gated_clamped(const void* x, const void* w, void* out, int M, int inter, int K, int ldx, float limit, float alpha,
-                                           int* error, cudaStream_t stream) {
-    return linear_tcgen05_gated_impl(x, w, out, M, inter, K, ldx, 4, error, stream, limit, alpha);
-}
-
 static int linear_tcgen05_gated_impl(const void* x, const void* w, void* out, int M, int inter, int K, int ldx, int act, int* error,
-                                     cudaStream_t stream, float limit, float alpha) {
+                                     cudaStream_t stream) {
     if (M <= 0 || inter <= 0) return VK_OK;
     if (K <= 0 || ldx < K || !error || K % 8 != 0 || ldx % 8 != 0 || inter % 8 != 0) return VK_BAD_SHAPE;
     if (((uintptr_t)x % 16) || ((uintptr_t)w % 16) || ((uintptr_t)out % 16)) return VK_BAD_ALIGNMENT;
@@ -857,8 +837,6 @@ static int linear_tcgen05_gated_impl(const void* x, const void* w, void* out, in
     TcExtra ex{};
     ex.inter = inter;
     ex.act = act;
-    ex.limit = limit;
-    ex.alpha = alpha;
     if (wide_takes(M, inter, K, TW_BN / 2)) {
         // Tiles of 128 x 96 output columns (192 weight rows) where they come out sooner than tiles of 128 x 128: a block
         // walks through ceil(tiles / blocks) tiles, and at the 135M and 360M sizes the last round of the wider tile is

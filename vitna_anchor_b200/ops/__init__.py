@@ -1246,16 +1246,8 @@ def residual_norm_step(x: torch.Tensor, y: Optional[torch.Tensor], w: Optional[t
 
 def linear_glu_clamped(x: torch.Tensor, w_gate_up: torch.Tensor, gu: torch.Tensor, out: torch.Tensor, limit: float, alpha: float) -> torch.Tensor:
     """out = g sigmoid(alpha g) (u + 1) with g = min(x @ w_gate.T, limit), u = clamp(x @ w_up.T, -limit, limit) for the two matrices
-    stacked by rows.  In bfloat16 with more rows than the few-rows products take it is the epilogue of the tcgen05 product (gate and
-    up rounded to bfloat16 first, as the product alone would store them); elsewhere the product writes gu [T, 2I] and glu_clamped follows."""
-    M, K = x.shape
-    inter = w_gate_up.shape[0] // 2
-    if (x.dtype == torch.bfloat16 and w_gate_up.dtype == torch.bfloat16 and w_gate_up.shape == (2 * inter, K) and tuple(out.shape) == (M, inter)
-            and out.dtype == x.dtype and out.is_contiguous() and w_gate_up.is_contiguous() and M > SKINNY_MAX_ROWS and inter % 8 == 0
-            and tcgen05_takes(x, w_gate_up) and out.data_ptr() % 16 == 0):
-        _check(lib().vk_linear_tcgen05_gated_clamped(_p(x), _p(w_gate_up), _p(out), M, inter, K, x.stride(0), ctypes.c_float(limit),
-                                                     ctypes.c_float(alpha), _p(error_word()), _stream()), "linear_tcgen05_gated")
-        return out
+    stacked by rows: the product writes gu [T, 2I] and glu_clamped follows.  (As one more case of the gated epilogue shared by the
+    tcgen05 products it slowed that epilogue's silu case, which the Llama models' prompts run, by three quarters; it stays a launch.)"""
     return glu_clamped(linear(x, w_gate_up, gu, LINEAR_SAME), out, limit, alpha)
 
 
