@@ -515,7 +515,7 @@ def test_the_output_norm_step_and_the_clamped_activation():
         g_, u_ = np.minimum(g_, 1.25), np.clip(u_, -1.25, 1.25)          # the gate is clamped from above only
         assert (g_ < -1.25).any()
         assert np.abs(out.float().cpu().numpy() - g_ * PM.sigmoid(1.702 * g_) * (u_ + 1)).max() < tol * 4
-    # as the epilogue of the tensor-core product (more rows than the few-rows products take; a narrow and a wide shape)
+    # product and activation together, at rows and sizes that the tensor-core products take (a narrow and a wide shape)
     for (T, K, inter) in ((200, 64, 72), (640, 512, 1024)):
         x = _dev(rng.standard_normal((T, K)), torch.bfloat16)
         w = _dev(rng.standard_normal((2 * inter, K)) * 2 * K ** -0.5, torch.bfloat16)
