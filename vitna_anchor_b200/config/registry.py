@@ -70,3 +70,7 @@ def _register_builtin() -> None:
     from . import manatar as _mtc
     register_architecture(Architecture(_mtc.ARCHITECTURE, _mtc.ManatarConfig.from_dict, _mt.manatar_manifest, _mt.build_manatar,
                                        _mt.is_norm_weight), replace=True)
+    from ..models import tinevik as _tv
+    from . import tinevik as _tvc
+    register_architecture(Architecture(_tvc.ARCHITECTURE, _tvc.TinevikConfig.from_dict, _tv.tinevik_manifest, _tv.build_tinevik,
+                                       _tv.is_norm_weight), replace=True)

@@ -2,6 +2,7 @@
 //
 //  experts_route     one block a token: logits z = W_r x + b in float32 (a warp a logit), the `top` largest (of equal logits the lower
 //                    index), weights = softmax over the chosen logits alone.  Writes ids [tokens][top] and weights [tokens][top].
+//  experts_route_table  ids[token][k] = table[token id][k], every weight 1 / top: the experts of a token are a function of its id.
 //  experts_gate_up   act[token, k] = f(W_gate,e x) * (W_up,e x) for the token's k-th expert e; a warp an output column, the token's row
 //                    in shared memory.  f is one of the epilogues' activations.
 //  experts_down      y[token] += sum_k weight_k W_down,e_k act[token, k], the experts of a token summed in the order of its list, so
@@ -72,10 +73,25 @@ __global__ void __launch_bounds__(128) experts_route_kernel(const T* __restrict_
     }
 }
 
+__global__ void __launch_bounds__(256) experts_route_table_kernel(const int32_t* __restrict__ tokens, const int32_t* __restrict__ table, int vocab,
+                                                                  int table_top, int E, int top, int32_t* __restrict__ ids, float* __restrict__ wts, int n) {
+    dependency_wait();
+    let_dependents_start();
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const int t = i / top, k = i - t * top;
+    int id = tokens[t];
+    id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
+    int e = table[(size_t)id * table_top + k];
+    ids[i] = e < 0 ? 0 : (e >= E ? E - 1 : e);         // a table that names no expert of the layer: stay inside the weights
+    wts[i] = 1.0f / (float)top;
+}
+
 // grid (pairs, column groups); a warp a column
 template <typename T>
 __global__ void __launch_bounds__(256) experts_gate_up_kernel(const T* __restrict__ x, int width, const T* __restrict__ wgu, int ff, int top,
-                                                              const int32_t* __restrict__ ids, int act, T* __restrict__ out) {
+                                                              const int32_t* __restrict__ ids, int act, float limit, float alpha,
+                                                              T* __restrict__ out) {
     extern __shared__ float xs[];                       // [width]
     dependency_wait();
     let_dependents_start();
@@ -96,7 +112,16 @@ __global__ void __launch_bounds__(256) experts_gate_up_kernel(const T* __restric
         }
         ag = warp_sum(ag);
         au = warp_sum(au);
-        if (lane == 0) out[(size_t)p * ff + c] = from_f32<T>(activate_rt(act, ag) * au);
+        if (lane == 0) {
+            float r;
+            if (act == 4) {                             // the clamped form: min(g, L) sigmoid(alpha min(g, L)) (clamp(u, -L, L) + 1)
+                const float g = fminf(ag, limit), u = fminf(fmaxf(au, -limit), limit);
+                r = (g / (1.0f + expf(-alpha * g))) * (u + 1.0f);
+            } else {
+                r = activate_rt(act, ag) * au;
+            }
+            out[(size_t)p * ff + c] = from_f32<T>(r);
+        }
     }
 }
 
@@ -248,12 +273,21 @@ VK_API int vk_experts_route(const void* x, int width, const float* wr, const flo
                             ids, wts);
 }
 
+// tokens int32 [n_tokens] (token ids); table int32 [vocab][table_top], table_top >= top; ids int32 [n_tokens][top], wts float32 [n_tokens][top].
+VK_API int vk_experts_route_table(const int32_t* tokens, const int32_t* table, int vocab, int table_top, int E, int top, int32_t* ids, float* wts,
+                                  int n_tokens, cudaStream_t stream) {
+    if (n_tokens <= 0) return VK_OK;
+    if (vocab <= 0 || E <= 0 || top <= 0 || top > table_top) return VK_BAD_SHAPE;
+    const int n = n_tokens * top;
+    return launch_dependent(experts_route_table_kernel, dim3((n + 255) / 256), dim3(256), 0, stream, tokens, table, vocab, table_top, E, top, ids, wts, n);
+}
+
 // wgu [E][2 ff][width] (an expert's gate rows, then its up rows) in dtype; out [tokens * top][ff] in dtype.  act: 0 none, 1 gelu (erf),
-// 2 gelu (tanh), 3 silu.
-VK_API int vk_experts_gate_up(const void* x, int width, const void* wgu, int ff, int top, const int32_t* ids, int act, void* out, int tokens,
-                              int dtype, cudaStream_t stream) {
+// 2 gelu (tanh), 3 silu, 4 the clamped form min(g, limit) sigmoid(alpha min(g, limit)) (clamp(u, -limit, limit) + 1).
+VK_API int vk_experts_gate_up(const void* x, int width, const void* wgu, int ff, int top, const int32_t* ids, int act, float limit, float alpha,
+                              void* out, int tokens, int dtype, cudaStream_t stream) {
     if (tokens <= 0) return VK_OK;
-    if (width <= 0 || ff <= 0 || top <= 0) return VK_BAD_SHAPE;
+    if (width <= 0 || ff <= 0 || top <= 0 || act < 0 || act > 4 || (act == 4 && !(limit > 0.0f))) return VK_BAD_SHAPE;
     const size_t smem = (size_t)width * sizeof(float);
     if (smem > 48 * 1024) return VK_TOO_LARGE;
     int gy = (ff + 7) / 8;
@@ -261,9 +295,9 @@ VK_API int vk_experts_gate_up(const void* x, int width, const void* wgu, int ff,
     dim3 grid(tokens * top, gy);
     if (dtype == 0)
         return launch_dependent(experts_gate_up_kernel<float>, grid, dim3(256), smem, stream, (const float*)x, width, (const float*)wgu, ff, top, ids, act,
-                                (float*)out);
+                                limit, alpha, (float*)out);
     return launch_dependent(experts_gate_up_kernel<__nv_bfloat16>, grid, dim3(256), smem, stream, (const __nv_bfloat16*)x, width,
-                            (const __nv_bfloat16*)wgu, ff, top, ids, act, (__nv_bfloat16*)out);
+                            (const __nv_bfloat16*)wgu, ff, top, ids, act, limit, alpha, (__nv_bfloat16*)out);
 }
 
 // act [tokens * top][ff] and wd [E][width][ff] in dtype; y float32 [tokens][width] is added to.

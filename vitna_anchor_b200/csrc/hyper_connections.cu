@@ -110,6 +110,15 @@ __global__ void activation_kernel(const T* x, T* out, size_t n) {       // out m
         out[i] = from_f32<T>(activate<KIND>(to_f32<T>(x[i])));
 }
 
+// f(z) = a_pos z^2 + z/2 for z > 0, a_neg (e^z - 1 - z) + z/2 otherwise: an activation with two numbers of its own
+template <typename T>
+__global__ void xielu_kernel(const T* x, T* out, size_t n, float a_pos, float a_neg) {       // out may be x
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const float z = to_f32<T>(x[i]);
+        out[i] = from_f32<T>(z > 0.0f ? fmaf(a_pos * z, z, 0.5f * z) : fmaf(a_neg, expm1f(z) - z, 0.5f * z));
+    }
+}
+
 }  // namespace vk
 
 using namespace vk;
@@ -170,4 +179,14 @@ static int launch_activation(const void* x, void* out, size_t n, int kind, cudaS
 VK_API int vk_activation(const void* x, void* out, size_t n, int kind, int dtype, cudaStream_t stream) {
     if (n == 0) return VK_OK;
     return dtype == 0 ? launch_activation<float>(x, out, n, kind, stream) : launch_activation<__nv_bfloat16>(x, out, n, kind, stream);
+}
+
+// out = a_pos x^2 + x/2 where x > 0, a_neg (exp(x) - 1 - x) + x/2 elsewhere (out may be x)
+VK_API int vk_xielu(const void* x, void* out, size_t n, float a_pos, float a_neg, int dtype, cudaStream_t stream) {
+    if (n == 0) return VK_OK;
+    size_t g = (n + 255) / 256;
+    const int grid = (int)(g < 1 ? 1 : (g > 148 * 16 ? 148 * 16 : g));
+    if (dtype == 0) xielu_kernel<float><<<grid, 256, 0, stream>>>((const float*)x, (float*)out, n, a_pos, a_neg);
+    else xielu_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)out, n, a_pos, a_neg);
+    return launch_status();
 }

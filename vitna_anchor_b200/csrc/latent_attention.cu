@@ -104,9 +104,61 @@ __global__ void __launch_bounds__(256) head_gate_kernel(T* __restrict__ x, const
     }
 }
 
+// The values' expansion behind the attention, for a gate that acts on every value: out[t][h][d] = (sum_r W[h][r][d] lat[t][h][r]) *
+// sigmoid(gate[t][h vd + d]).  W is stored [H][rank][vd], so that neighbouring threads read neighbouring values.  A block takes LX_TOKENS
+// tokens of one head (a weight is read once for all of them); a sum runs over the rank in one order whatever the batch.
+constexpr int LX_TOKENS = 8;
+template <typename T>
+__global__ void __launch_bounds__(128) latent_expand_gate_kernel(const T* __restrict__ lat, const T* __restrict__ w, const float* __restrict__ gates, int N,
+                                                                 int gate_off, int H, int rank, int vd, T* __restrict__ out, int tokens) {
+    extern __shared__ float lx_sh[];                    // [LX_TOKENS][rank]
+    dependency_wait();
+    let_dependents_start();
+    const int h = blockIdx.y, t0 = blockIdx.x * LX_TOKENS, cnt = min(LX_TOKENS, tokens - t0);
+    for (int i = threadIdx.x; i < LX_TOKENS * rank; i += blockDim.x) {
+        const int t = i / rank, r = i - t * rank;
+        lx_sh[i] = t < cnt ? to_f32<T>(lat[((size_t)(t0 + t) * H + h) * rank + r]) : 0.0f;
+    }
+    __syncthreads();
+    const T* wh = w + (size_t)h * rank * vd;
+    for (int d = threadIdx.x; d < vd; d += blockDim.x) {
+        float acc[LX_TOKENS];
+#pragma unroll
+        for (int t = 0; t < LX_TOKENS; t++) acc[t] = 0.0f;
+        for (int r = 0; r < rank; r++) {
+            const float wv = to_f32<T>(wh[(size_t)r * vd + d]);
+#pragma unroll
+            for (int t = 0; t < LX_TOKENS; t++) acc[t] = fmaf(lx_sh[t * rank + r], wv, acc[t]);
+        }
+#pragma unroll
+        for (int t = 0; t < LX_TOKENS; t++)
+            if (t < cnt) {
+                float v = acc[t];
+                if (gates) v *= 1.0f / (1.0f + expf(-gates[(size_t)(t0 + t) * N + gate_off + h * vd + d]));
+                out[((size_t)(t0 + t) * H + h) * vd + d] = from_f32<T>(v);
+            }
+    }
+}
+
 }  // namespace vk
 
 using namespace vk;
+
+// lat [tokens][H][rank], w [H][rank][vd] and out [tokens][H][vd] in dtype; gates float32 [tokens][N] with the gate's values at gate_off
+// (null: no gate).
+VK_API int vk_latent_expand_gate(const void* lat, const void* w, const float* gates, int N, int gate_off, int H, int rank, int vd, void* out, int tokens,
+                                 int dtype, cudaStream_t stream) {
+    if (tokens <= 0) return VK_OK;
+    if (H <= 0 || rank <= 0 || vd <= 0 || (gates && (gate_off < 0 || gate_off + H * vd > N))) return VK_BAD_SHAPE;
+    const size_t smem = (size_t)LX_TOKENS * rank * sizeof(float);
+    if (smem > 48 * 1024 || H > 65535) return VK_TOO_LARGE;
+    dim3 grid((tokens + LX_TOKENS - 1) / LX_TOKENS, H);
+    if (dtype == 0)
+        return launch_dependent(latent_expand_gate_kernel<float>, grid, dim3(128), smem, stream, (const float*)lat, (const float*)w, gates, N, gate_off, H,
+                                rank, vd, (float*)out, tokens);
+    return launch_dependent(latent_expand_gate_kernel<__nv_bfloat16>, grid, dim3(128), smem, stream, (const __nv_bfloat16*)lat, (const __nv_bfloat16*)w,
+                            gates, N, gate_off, H, rank, vd, (__nv_bfloat16*)out, tokens);
+}
 
 // proj float32 [tokens][N]: columns 0..q_rank-1 the query latent, kv_off.. the key-value latent and the shared key part
 // (kv_off < 0: none).  cq [tokens][q_rank] and cache in dtype.  slot [tokens] (-1: no write).

@@ -84,6 +84,82 @@ __global__ void __launch_bounds__(256) residual_norm_step_kernel(float* __restri
     }
 }
 
+// The step between two sublayers of a layer with a norm before AND behind each sublayer (layer norms with weight and bias):
+//   x += LN(y; w_post, b_post),  y = 0,  xn = LN(x; w_next, b_next) in the compute dtype
+// (w_post null: nothing is added, y is only zeroed; w_next null: no normed output).  A block a row; the row's values stay in
+// registers (up to SW_KEEP a thread) between the sums, which meet in an order that depends on the width alone.
+constexpr int SW_THREADS = 128;
+constexpr int SW_KEEP = 16;
+template <typename T>
+__global__ void __launch_bounds__(SW_THREADS) sandwich_step_kernel(float* __restrict__ x, float* __restrict__ y, const float* __restrict__ wp,
+                                                                   const float* __restrict__ bp, const float* __restrict__ wn,
+                                                                   const float* __restrict__ bn, T* __restrict__ xn, int n, float eps) {
+    __shared__ float scratch[32];
+    dependency_wait();
+    let_dependents_start();
+    const size_t base = (size_t)blockIdx.x * n;
+    const int tid = threadIdx.x;
+    float v[SW_KEEP];
+    if (wp) {
+        float sum = 0.0f;
+#pragma unroll
+        for (int j = 0; j < SW_KEEP; j++) {
+            const int i = tid + j * SW_THREADS;
+            v[j] = i < n ? y[base + i] : 0.0f;
+            sum += v[j];
+        }
+        for (int i = tid + SW_KEEP * SW_THREADS; i < n; i += SW_THREADS) sum += y[base + i];
+        const float mean = block_sum(sum, scratch) / (float)n;
+        float ss = 0.0f;
+#pragma unroll
+        for (int j = 0; j < SW_KEEP; j++) {
+            const int i = tid + j * SW_THREADS;
+            if (i < n) { const float d = v[j] - mean; ss = fmaf(d, d, ss); }
+        }
+        for (int i = tid + SW_KEEP * SW_THREADS; i < n; i += SW_THREADS) { const float d = y[base + i] - mean; ss = fmaf(d, d, ss); }
+        const float inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)n + eps);
+#pragma unroll
+        for (int j = 0; j < SW_KEEP; j++) {
+            const int i = tid + j * SW_THREADS;
+            if (i < n) {
+                v[j] = x[base + i] + fmaf((v[j] - mean) * inv, wp[i], bp[i]);
+                x[base + i] = v[j];
+                y[base + i] = 0.0f;
+            }
+        }
+        for (int i = tid + SW_KEEP * SW_THREADS; i < n; i += SW_THREADS) {
+            x[base + i] += fmaf((y[base + i] - mean) * inv, wp[i], bp[i]);
+            y[base + i] = 0.0f;
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < SW_KEEP; j++) {
+            const int i = tid + j * SW_THREADS;
+            v[j] = i < n ? x[base + i] : 0.0f;
+            if (y && i < n) y[base + i] = 0.0f;
+        }
+        if (y) for (int i = tid + SW_KEEP * SW_THREADS; i < n; i += SW_THREADS) y[base + i] = 0.0f;
+    }
+    if (!wn) return;
+    float sum = 0.0f;
+#pragma unroll
+    for (int j = 0; j < SW_KEEP; j++) sum += (tid + j * SW_THREADS < n) ? v[j] : 0.0f;
+    for (int i = tid + SW_KEEP * SW_THREADS; i < n; i += SW_THREADS) sum += x[base + i];
+    const float mean = block_sum(sum, scratch) / (float)n;
+    float ss = 0.0f;
+#pragma unroll
+    for (int j = 0; j < SW_KEEP; j++)
+        if (tid + j * SW_THREADS < n) { const float d = v[j] - mean; ss = fmaf(d, d, ss); }
+    for (int i = tid + SW_KEEP * SW_THREADS; i < n; i += SW_THREADS) { const float d = x[base + i] - mean; ss = fmaf(d, d, ss); }
+    const float inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)n + eps);
+#pragma unroll
+    for (int j = 0; j < SW_KEEP; j++) {
+        const int i = tid + j * SW_THREADS;
+        if (i < n) xn[base + i] = from_f32<T>(fmaf((v[j] - mean) * inv, wn[i], bn[i]));
+    }
+    for (int i = tid + SW_KEEP * SW_THREADS; i < n; i += SW_THREADS) xn[base + i] = from_f32<T>(fmaf((x[base + i] - mean) * inv, wn[i], bn[i]));
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256) glu_clamped_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter, float limit, float alpha) {
     dependency_wait();
@@ -132,4 +208,16 @@ VK_API int vk_glu_clamped(const void* gu, void* out, int tokens, int inter, floa
     if (dtype == 0) return launch_dependent(glu_clamped_kernel<float>, dim3(tokens), dim3(256), 0, stream, (const float*)gu, (float*)out, inter, limit, alpha);
     return launch_dependent(glu_clamped_kernel<__nv_bfloat16>, dim3(tokens), dim3(256), 0, stream, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, inter,
                             limit, alpha);
+}
+
+// x, y float32 [rows][n]; w_post, b_post float32 [n] (both null: nothing is added); w_next, b_next float32 [n] and xn [rows][n] in dtype
+// (all null: no normed output).
+VK_API int vk_sandwich_step(float* x, float* y, const float* w_post, const float* b_post, const float* w_next, const float* b_next, void* xn, int rows,
+                            int n, float eps, int dtype, cudaStream_t stream) {
+    if (rows <= 0) return VK_OK;
+    if (n <= 0 || (w_post && (!y || !b_post)) || (w_next && (!b_next || !xn))) return VK_BAD_SHAPE;
+    if (dtype == 0)
+        return launch_dependent(sandwich_step_kernel<float>, dim3(rows), dim3(SW_THREADS), 0, stream, x, y, w_post, b_post, w_next, b_next, (float*)xn, n, eps);
+    return launch_dependent(sandwich_step_kernel<__nv_bfloat16>, dim3(rows), dim3(SW_THREADS), 0, stream, x, y, w_post, b_post, w_next, b_next,
+                            (__nv_bfloat16*)xn, n, eps);
 }

@@ -55,7 +55,9 @@ def random_model_on_device(config_json: Mapping[str, Any], seed: int, dtype="bfl
             continue
         shape = tuple(w.free_size if d is None else d for d in w.shape)
         kind = arch.is_norm_weight(w.name)
-        if kind == "identity":
+        if not w.floating:
+            weights[w.name] = torch.rand((shape[0], w.int_range), device=device, generator=gen).argsort(dim=1)[:, :shape[1]].to(torch.int32)
+        elif kind == "identity":
             weights[w.name] = torch.eye(shape[0], dtype=torch.float32, device=device)
         elif kind:
             weights[w.name] = torch.ones(shape, dtype=torch.float32, device=device)

@@ -1376,10 +1376,28 @@ def experts_route(x: torch.Tensor, w_router: torch.Tensor, b_router: Optional[to
     _check(lib().vk_experts_route(_p(x), W, _p(w_router), _p(b_router), w_router.shape[0], top, _p(ids), _p(wts), T, _dt(x), _stream()), "experts_route")
 
 
+def experts_route_table(tokens: torch.Tensor, table: torch.Tensor, E: int, top: int, ids: torch.Tensor, wts: torch.Tensor) -> None:
+    """ids [T, top] = table[token id, :top] (int32 [vocab, >= top]); every weight 1 / top."""
+    _req(tokens, "tokens", torch.int32, 1); _req(table, "table", torch.int32, 2); _req(ids, "ids", torch.int32, 2); _req(wts, "wts", torch.float32, 2)
+    T = tokens.shape[0]
+    if table.shape[1] < top or ids.shape != (T, top) or wts.shape != (T, top):
+        raise KernelError("experts_route_table: shapes do not fit")
+    _check(lib().vk_experts_route_table(_p(tokens), _p(table), table.shape[0], table.shape[1], E, top, _p(ids), _p(wts), T, _stream()),
+           "experts_route_table")
+
+
+def _expert_act(activation: str, what: str) -> int:
+    if activation == "clamped":
+        return 4
+    if activation not in _EPILOGUE_ACT:
+        raise KernelError(f"{what}: {activation!r} is not one of {sorted(_EPILOGUE_ACT) + ['clamped']}")
+    return _EPILOGUE_ACT[activation]
+
+
 def experts_apply(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, act_buf: torch.Tensor,
-                  y: torch.Tensor, activation: str = "silu") -> torch.Tensor:
+                  y: torch.Tensor, activation: str = "silu", limit: float = 0.0, alpha: float = 1.702) -> torch.Tensor:
     """y [T, W] (float32) += sum_k wts[t, k] W_down,e (act(W_gate,e x) * W_up,e x), e = ids[t, k]; w_gate_up [E, 2 ff, W], w_down [E, W, ff]
-    in x's dtype; act_buf [T * top, ff] in x's dtype."""
+    in x's dtype; act_buf [T * top, ff] in x's dtype.  activation "clamped": min(g, limit) sigmoid(alpha min(g, limit)) (clamp(u) + 1)."""
     _req(x, "x", dims=2); _req(w_gate_up, "w_gate_up", x.dtype, 3); _req(w_down, "w_down", x.dtype, 3); _req(y, "y", torch.float32, 2)
     _req(act_buf, "act_buf", x.dtype, 2)
     T, W = x.shape
@@ -1387,10 +1405,9 @@ def experts_apply(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor
     ff, top = two_ff // 2, ids.shape[1]
     if w_gate_up.shape != (E, 2 * ff, W) or w_down.shape != (E, W, ff) or y.shape != (T, W) or act_buf.shape != (T * top, ff):
         raise KernelError("experts_apply: shapes do not fit")
-    if activation not in _EPILOGUE_ACT:
-        raise KernelError(f"experts_apply: {activation!r} is not one of {sorted(_EPILOGUE_ACT)}")
-    _check(lib().vk_experts_gate_up(_p(x), W, _p(w_gate_up), ff, top, _p(ids), _EPILOGUE_ACT[activation], _p(act_buf), T, _dt(x), _stream()),
-           "experts_gate_up")
+    act = _expert_act(activation, "experts_apply")
+    _check(lib().vk_experts_gate_up(_p(x), W, _p(w_gate_up), ff, top, _p(ids), act, ctypes.c_float(limit), ctypes.c_float(alpha), _p(act_buf), T,
+                                    _dt(x), _stream()), "experts_gate_up")
     _check(lib().vk_experts_down(_p(act_buf), ff, _p(w_down), W, top, _p(ids), _p(wts), _p(y), T, _dt(x), _stream()), "experts_down")
     return y
 
@@ -1412,10 +1429,12 @@ def experts_grouped_takes(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torc
 
 def experts_apply_grouped(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, pos: torch.Tensor,
                           row_token: torch.Tensor, tile_group: torch.Tensor, xs: torch.Tensor, act_buf: torch.Tensor, o: torch.Tensor,
-                          y: torch.Tensor, activation: str = "silu") -> torch.Tensor:
+                          y: torch.Tensor, activation: str = "silu", limit: float = 0.0, alpha: float = 1.702,
+                          gu_buf: Optional[torch.Tensor] = None) -> torch.Tensor:
     """experts_apply on the tensor cores: the tokens' copies are put expert by expert into xs [rows, W] (rows =
     experts_grouped_rows(T, top, E); pos [T, top], row_token [rows], tile_group [rows / 128] int32), two products of row groups give
-    act_buf [rows, ff] (bfloat16) and o [rows, W] (float32), and y [T, W] (float32) += the weighted rows of each token."""
+    act_buf [rows, ff] (bfloat16) and o [rows, W] (float32), and y [T, W] (float32) += the weighted rows of each token.
+    activation "clamped" (with gu_buf [rows, 2 ff] bfloat16): the first product leaves gate and up, and glu_clamped follows."""
     _req(x, "x", torch.bfloat16, 2); _req(y, "y", torch.float32, 2); _req(o, "o", torch.float32, 2); _req(xs, "xs", torch.bfloat16, 2)
     _req(act_buf, "act_buf", torch.bfloat16, 2); _req(pos, "pos", torch.int32, 2); _req(row_token, "row_token", torch.int32, 1)
     _req(tile_group, "tile_group", torch.int32, 1)
@@ -1427,14 +1446,192 @@ def experts_apply_grouped(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torc
             or xs.shape != (rows, W) or act_buf.shape != (rows, ff) or o.shape != (rows, W) or pos.shape != (T, top) or row_token.shape != (rows,)
             or tile_group.shape != (rows // 128,)):
         raise KernelError("experts_apply_grouped: shapes do not fit")
-    if activation not in _EPILOGUE_ACT:
-        raise KernelError(f"experts_apply_grouped: {activation!r} is not one of {sorted(_EPILOGUE_ACT)}")
-    act = 0 if activation == "silu" else _EPILOGUE_ACT[activation]
+    act = _expert_act(activation, "experts_apply_grouped")
+    act = 0 if activation == "silu" else act
+    if act == 4:
+        if gu_buf is None or gu_buf.shape != (rows, 2 * ff):
+            raise KernelError("experts_apply_grouped: the clamped form needs gu_buf [rows, 2 ff]")
+        _req(gu_buf, "gu_buf", torch.bfloat16, 2)
     _check(lib().vk_experts_sort(_p(ids), T, top, E, rows, _p(pos), _p(row_token), _p(tile_group), _stream()), "experts_sort")
     _check(lib().vk_experts_gather(_p(x), W, _p(row_token), _p(xs), rows, _dt(x), _stream()), "experts_gather")
-    _check(lib().vk_linear_tcgen05_grouped(_p(xs), _p(w_gate_up), _p(act_buf), rows, ff, W, W, E, _p(tile_group), 0, 1, act, _p(error_word()),
-                                           _stream()), "linear_tcgen05_grouped")
+    if act == 4:
+        _check(lib().vk_linear_tcgen05_grouped(_p(xs), _p(w_gate_up), _p(gu_buf), rows, 2 * ff, W, W, E, _p(tile_group), 0, 0, 0, _p(error_word()),
+                                               _stream()), "linear_tcgen05_grouped")
+        glu_clamped(gu_buf, act_buf, limit, alpha)
+    else:
+        _check(lib().vk_linear_tcgen05_grouped(_p(xs), _p(w_gate_up), _p(act_buf), rows, ff, W, W, E, _p(tile_group), 0, 1, act, _p(error_word()),
+                                               _stream()), "linear_tcgen05_grouped")
     _check(lib().vk_linear_tcgen05_grouped(_p(act_buf), _p(w_down), _p(o), rows, W, ff, ff, E, _p(tile_group), 1, 0, 0, _p(error_word()),
                                            _stream()), "linear_tcgen05_grouped")
     _check(lib().vk_experts_combine(_p(o), W, top, _p(pos), _p(wts), _p(y), T, _stream()), "experts_combine")
     return y
+
+
+# ---------------------------------------------------------------------------
+# A norm before and behind each sublayer; an activation with two numbers of its own
+# ---------------------------------------------------------------------------
+
+def sandwich_step(x: torch.Tensor, y: Optional[torch.Tensor], post: Optional[tuple], nxt: Optional[tuple], xn: Optional[torch.Tensor],
+                  eps: float) -> Optional[torch.Tensor]:
+    """x += LN(y; post = (w, b)) and y = 0 (post None: y is only zeroed), then xn = LN(x; nxt = (w, b)) in xn's dtype (nxt None: none).
+    x, y float32 [T, n]; the weights float32 [n]."""
+    _req(x, "x", torch.float32, 2)
+    T, n = x.shape
+    if y is not None:
+        _req(y, "y", torch.float32, 2)
+        if y.shape != x.shape:
+            raise KernelError("sandwich_step: x and y differ in shape")
+    for pair in (post, nxt):
+        if pair is not None:
+            for v in pair:
+                _req(v, "a norm's weight", torch.float32, 1)
+                if v.shape[0] != n:
+                    raise KernelError("sandwich_step: a norm's weight does not fit the width")
+    if nxt is not None:
+        _req(xn, "xn", dims=2)
+        if xn.shape != x.shape:
+            raise KernelError("sandwich_step: xn does not fit x")
+    wp, bp = post if post is not None else (None, None)
+    wn, bn = nxt if nxt is not None else (None, None)
+    _check(lib().vk_sandwich_step(_p(x), _p(y), _p(wp), _p(bp), _p(wn), _p(bn), _p(xn if nxt is not None else None), T, n, ctypes.c_float(eps),
+                                  _dt(xn) if nxt is not None else 0, _stream()), "sandwich_step")
+    return xn if nxt is not None else None
+
+
+def linear_xielu(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, a_pos: float, a_neg: float) -> torch.Tensor:
+    """out = xielu(x @ w.T) in x's dtype: the product, then the activation in place."""
+    return xielu(linear(x, w, out, LINEAR_SAME), a_pos, a_neg)
+
+
+def xielu(x: torch.Tensor, a_pos: float, a_neg: float, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out = a_pos x^2 + x / 2 where x > 0, a_neg (exp(x) - 1 - x) + x / 2 elsewhere (in place unless out is given)."""
+    out = x if out is None else out
+    _req(x, "x"); _req(out, "out", x.dtype)
+    if out.numel() != x.numel():
+        raise KernelError("xielu: sizes differ")
+    _check(lib().vk_xielu(_p(x), _p(out), ctypes.c_size_t(x.numel()), ctypes.c_float(a_pos), ctypes.c_float(a_neg), _dt(x), _stream()), "xielu")
+    return out
+
+
+# ---------------------------------------------------------------------------
+# Gated linear attention
+# ---------------------------------------------------------------------------
+
+def gla_state_floats(H: int, dim: int, vdim: int) -> int:
+    return H * dim * vdim
+
+
+def gla_max_dim() -> int:
+    return int(lib().vk_gla_max_dim())
+
+
+def gla(proj: torch.Tensor, a_off: int, a2t: torch.Tensor, bias: torch.Tensor, tau: float, norm_w: torch.Tensor, eps: float, ctx,
+        state: torch.Tensor, decay: torch.Tensor, o: torch.Tensor, out: torch.Tensor, H: int, dim: int, vdim: int, gate_off: int) -> torch.Tensor:
+    """proj float32 [T, N] = q | k | v | ... with the gate's H vdim columns at gate_off and the decays' narrow half (rank = a2t.shape[0]
+    columns) at a_off; a2t float32 [rank, H dim], bias [H dim]; the recurrence S <- diag(a) S + k v^T, o = S^T q dim^-1/2 token after token
+    per segment from and into state [slots, H dim vdim]; decay float32 [T, H dim] and o float32 [T, H vdim] are scratch; out [T, H vdim] =
+    o / rms(o) per head * norm_w [vdim] * silu(gate) in out's dtype.  A batch of single tokens takes one launch for decays and step."""
+    _req(proj, "proj", torch.float32, 2); _req(a2t, "a2t", torch.float32, 2); _req(bias, "bias", torch.float32, 1); _req(norm_w, "norm_w", torch.float32, 1)
+    _req(state, "state", torch.float32); _req(decay, "decay", torch.float32, 2); _req(o, "o", torch.float32, 2); _req(out, "out", dims=2)
+    T, N = proj.shape
+    rank, C = a2t.shape
+    if (C != H * dim or bias.shape[0] != C or norm_w.shape[0] != vdim or N < max(2 * H * dim + H * vdim, a_off + rank, gate_off + H * vdim)
+            or decay.shape != (T, C) or o.shape != (T, H * vdim) or out.shape != (T, H * vdim) or state[0].numel() != gla_state_floats(H, dim, vdim)):
+        raise KernelError("gla: shapes do not fit the head counts")
+    L = lib()
+    if ctx.decode_only and not (proj.dtype == torch.float32 and out.dtype == torch.float32 and _float32_exact):
+        _check(L.vk_gla_decode(_p(proj), N, H, dim, vdim, a_off, rank, _p(a2t), _p(bias), ctypes.c_float(tau), _p(ctx.seg_starts), _p(ctx.seg_slots),
+                               _p(state), _p(o), ctx.num_segments, _stream()), "gla_decode")
+    else:
+        _check(L.vk_gla_prepare(_p(proj), N, a_off, rank, _p(a2t), _p(bias), ctypes.c_float(tau), C, _p(decay), T, _stream()), "gla_prepare")
+        _check(L.vk_gla_recurrence(_p(proj), N, H, dim, vdim, _p(decay), _p(ctx.seg_starts), _p(ctx.seg_slots), _p(state), _p(o), ctx.num_segments,
+                                   _stream()), "gla_recurrence")
+    _check(L.vk_gla_gate(_p(o), _p(proj), N, gate_off, _p(norm_w), ctypes.c_float(eps), H, vdim, _p(out), T, _dt(out), _stream()), "gla_gate")
+    return out
+
+
+# ---------------------------------------------------------------------------
+# Attention with capped, mixed scores and rotated values
+# ---------------------------------------------------------------------------
+
+def mixed_attn_prepare(proj: torch.Tensor, positions: torch.Tensor, slot_mapping: Optional[torch.Tensor], q_norm: Optional[torch.Tensor],
+                       k_norm: Optional[torch.Tensor], eps: float, freq: Optional[torch.Tensor], dims: int, vfreq: Optional[torch.Tensor],
+                       q_out: torch.Tensor, cache_layer: Optional[torch.Tensor], nh: int, nkv: int, hd: int, vd: int, page_size: int) -> torch.Tensor:
+    """From the float32 row [q | k | v] of the first product: q and k heads / rms * weight (eps < 0: no norm), the first `dims` values turned
+    in pairs (i, i + dims / 2) by position * freq[i]; v turned over all its pairs by position * vfreq[m] (None: not); q to q_out, k and v
+    into the layer's pages at slot_mapping (-1: no write)."""
+    _req(proj, "proj", torch.float32, 2); _req(positions, "positions", torch.int32, 1); _req(q_out, "q_out", dims=2)
+    T, N = proj.shape
+    if N < (nh + nkv) * hd + nkv * vd or q_out.shape != (T, nh * hd) or positions.shape[0] < T:
+        raise KernelError("mixed_attn_prepare: shapes do not fit the head counts")
+    for v, n, name in ((q_norm, hd, "q_norm"), (k_norm, hd, "k_norm"), (freq, dims // 2, "freq"), (vfreq, vd // 2, "vfreq")):
+        if v is not None:
+            _req(v, name, torch.float32, 1)
+            if v.shape[0] != n:
+                raise KernelError(f"mixed_attn_prepare: {name} has {v.shape[0]} values, expected {n}")
+    if dims and freq is None:
+        raise KernelError("mixed_attn_prepare: a rotation needs its frequencies")
+    if cache_layer is not None:
+        _req(cache_layer, "cache_layer", q_out.dtype); _req(slot_mapping, "slot_mapping", torch.int32, 1)
+        if _page_size_of(cache_layer, nkv, hd, vd) != page_size or slot_mapping.shape[0] < T:
+            raise KernelError("mixed_attn_prepare: the cache layer does not fit the page size")
+    _check(lib().vk_mixed_attn_prepare(_p(proj), N, _p(positions), _p(slot_mapping if cache_layer is not None else None), _p(q_norm), _p(k_norm),
+                                       ctypes.c_float(eps), _p(freq if dims else None), dims, _p(vfreq), _p(q_out), _p(cache_layer), T, nh, nkv, hd, vd,
+                                       page_size, _dt(q_out), _stream()), "mixed_attn_prepare")
+    return q_out
+
+
+def attention_mixed_rows(q: torch.Tensor, cache_layer: torch.Tensor, block_tables: torch.Tensor, token_seg: torch.Tensor, positions: torch.Tensor,
+                         out: torch.Tensor, nh: int, nkv: int, hd: int, vd: int, page_size: int, scale: float, cap: float = 0.0,
+                         mix: Optional[torch.Tensor] = None, vfreq: Optional[torch.Tensor] = None, window: int = 0,
+                         tok_list: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Causal attention of every token (or of those in tok_list) over its request's pages with all heads of a token in one block:
+    scores scale * q.k, capped by cap * tanh(. / cap) (cap <= 0: not), mixed over the heads by mix [nh, nh] (None: not), softmax,
+    the weighted sum of the values, turned back by the query's position with vfreq (None: not).  Any sizes, float32 arithmetic."""
+    _req(q, "q", dims=2); _req(cache_layer, "cache_layer", q.dtype); _req(block_tables, "block_tables", torch.int32, 2)
+    _req(token_seg, "token_seg", torch.int32, 1); _req(positions, "positions", torch.int32, 1); _req(out, "out", q.dtype, 2)
+    T = q.shape[0]
+    if q.shape[1] != nh * hd or out.shape != (T, nh * vd) or _page_size_of(cache_layer, nkv, hd, vd) != page_size:
+        raise KernelError("attention_mixed_rows: shapes do not fit the head counts")
+    if mix is not None:
+        _req(mix, "mix", torch.float32, 2)
+        if mix.shape != (nh, nh):
+            raise KernelError("attention_mixed_rows: the mixing matrix is not [heads, heads]")
+    if vfreq is not None:
+        _req(vfreq, "vfreq", torch.float32, 1)
+        if vfreq.shape[0] != vd // 2:
+            raise KernelError("attention_mixed_rows: the values' frequencies do not fit their size")
+    n = T
+    if tok_list is not None:
+        _req(tok_list, "tok_list", torch.int32, 1)
+        n = tok_list.shape[0]
+    _check(lib().vk_attention_mixed_rows(_p(q), _p(cache_layer), _p(block_tables), _p(token_seg), _p(positions), _p(tok_list), _p(out), n, nh, nkv, hd, vd,
+                                         page_size, block_tables.shape[1], ctypes.c_float(scale), ctypes.c_float(cap), _p(mix), _p(vfreq), window,
+                                         _dt(q), _stream()), "attention_mixed_rows")
+    return out
+
+
+def attention_mixed(q: torch.Tensor, pages: torch.Tensor, meta, ctx, out: torch.Tensor, nh: int, nkv: int, hd: int, vd: int, page_size: int,
+                    scale: float, cap: float = 0.0, mix: Optional[torch.Tensor] = None, vfreq: Optional[torch.Tensor] = None,
+                    window: int = 0) -> torch.Tensor:
+    """The attention with capped, mixed scores of a mixed batch over the paged cache; `meta` is the page group's GroupMeta."""
+    return attention_mixed_rows(q, pages, meta.block_tables, ctx.token_seg, ctx.positions, out, nh, nkv, hd, vd, page_size, scale, cap, mix,
+                                vfreq, window)
+
+
+def latent_expand_gate(lat: torch.Tensor, w: torch.Tensor, gates: Optional[torch.Tensor], gate_off: int, H: int, rank: int, vd: int,
+                       out: torch.Tensor) -> torch.Tensor:
+    """out[t, h, :] = (w[h]^T lat[t, h, :]) * sigmoid(gates[t, gate_off + h vd : ...]); lat [T, H rank], w [H, rank, vd] and out [T, H vd] in one
+    dtype, gates float32 [T, N] (None: no gate)."""
+    _req(lat, "lat", dims=2); _req(w, "w", lat.dtype, 3); _req(out, "out", lat.dtype, 2)
+    T = lat.shape[0]
+    if lat.shape[1] != H * rank or w.shape != (H, rank, vd) or out.shape != (T, H * vd):
+        raise KernelError("latent_expand_gate: shapes do not fit the head counts")
+    N = 0
+    if gates is not None:
+        _req(gates, "gates", torch.float32, 2)
+        N = gates.shape[1]
+        if gates.shape[0] != T:
+            raise KernelError("latent_expand_gate: the gates do not fit the tokens")
+    _check(lib().vk_latent_expand_gate(_p(lat), _p(w), _p(gates), N, gate_off, H, rank, vd, _p(out), T, _dt(lat), _stream()), "latent_expand_gate")
+    return out

@@ -2,7 +2,10 @@
 (engine/src/model.c:906-972).
 
 Output-norm residual block: x += m * norm1(mixer(x)); x += m * norm2(feed_forward(x)): the sublayers read the residual
-stream as it is and the norm sits on what they give."""
+stream as it is and the norm sits on what they give.
+
+Sandwich-norm residual block: x += post1(mixer(pre1(x))); x += post2(feed_forward(pre2(x))), the four norms layer norms with weight
+and bias."""
 from __future__ import annotations
 
 from typing import Optional
@@ -74,3 +77,40 @@ class OutputNormBlock(Block):
         self.ffn.forward(xc, ctx, y)
         w, eps = self.ffn_norm.as_rms()
         ops.residual_norm_step(x, y, w, copy, eps, self.mult)
+
+
+class SandwichNormBlock(Block):
+    """x <- x + post(sublayer(pre(x))) for the mixer and then (unless absent) the feed-forward; the four norms are layer norms with
+    weight and bias (anything with .weight, .bias and .eps of the LayerNorm part).
+
+    The sublayers keep the framework's contract (they ADD their result into a float32 buffer): the buffer is a zeroed row y, and ONE
+    kernel between two sublayers norms y, sums it into the float32 residual row, zeroes y again and norms the new row for the next
+    sublayer.  The first kernel of a block only zeroes y and norms x; the last only sums (the next block's pre-norm may belong to
+    another kind of block)."""
+
+    def __init__(self, mixer_norm: Norm, mixer_post: Norm, mixer: Mixer, ffn_norm: Optional[Norm] = None, ffn_post: Optional[Norm] = None,
+                 ffn: Optional[FeedForward] = None):
+        if not ((ffn is None) == (ffn_norm is None) == (ffn_post is None)):
+            raise ValueError("a feed-forward and its two norms come together")
+        for n in (mixer_norm, mixer_post, ffn_norm, ffn_post):
+            if n is not None and not (hasattr(n, "weight") and hasattr(n, "bias") and hasattr(n, "eps")):
+                raise ValueError("the norms of this block are layer norms with weight and bias")
+        self.mixer_norm, self.mixer_post, self.mixer, self.ffn_norm, self.ffn_post, self.ffn = mixer_norm, mixer_post, mixer, ffn_norm, ffn_post, ffn
+
+    def tensors(self):
+        return [t for p in (self.mixer_norm, self.mixer_post, self.mixer, self.ffn_norm, self.ffn_post, self.ffn) if p is not None for t in p.tensors()]
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache: Optional[LayerCacheView], write_cache: bool = True) -> None:
+        T, W, ws = ctx.num_tokens, x.shape[1], ctx.workspace
+        y = ws.flat(f"sandwich.y/{W}", ws.max_tokens * W, torch.float32, zero=True)[:T * W].view(T, W)
+        xn = ws.rows("block.xn", T, W, ctx.dtype)
+        pair = lambda n: (n.weight, n.bias)
+        eps = self.mixer_norm.eps
+        ops.sandwich_step(x, y, None, pair(self.mixer_norm), xn, eps)
+        self.mixer.forward(xn, ctx, cache, y, write_cache)
+        if self.ffn is None:
+            ops.sandwich_step(x, y, pair(self.mixer_post), None, None, eps)
+            return
+        ops.sandwich_step(x, y, pair(self.mixer_post), pair(self.ffn_norm), xn, eps)
+        self.ffn.forward(xn, ctx, y)
+        ops.sandwich_step(x, y, pair(self.ffn_post), None, None, eps)

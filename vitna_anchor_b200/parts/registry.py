@@ -32,7 +32,9 @@ def make_part(kind: str, name: str, **params):
 
 def _register_builtin() -> None:
     from .attention import PagedAttention
-    from .block import OutputNormBlock, PreNormBlock
+    from .block import OutputNormBlock, PreNormBlock, SandwichNormBlock
+    from .gla import GatedLinearAttention
+    from .mixed_attention import MixedHeadAttention
     from .diff_attention import DiffAttention
     from .mlstm import MatrixLSTM
     from .delta import ChannelDeltaRule, GatedDeltaRule
@@ -47,6 +49,8 @@ def _register_builtin() -> None:
     register_part("mixer", "latent_attention", LatentAttention.from_matrices)
     register_part("mixer", "diff_attention", DiffAttention)
     register_part("mixer", "mlstm", MatrixLSTM)
+    register_part("mixer", "gla", GatedLinearAttention)
+    register_part("mixer", "mixed_attention", MixedHeadAttention)
     register_part("feed_forward", "clamped_glu", ClampedGLU)
     register_part("feed_forward", "routed_experts", RoutedExperts)
     register_part("feed_forward", "swiglu", SwiGLU)
@@ -58,6 +62,7 @@ def _register_builtin() -> None:
     register_part("position", "none", NoPositionEncoding)
     register_part("block", "pre_norm", PreNormBlock)
     register_part("block", "output_norm", OutputNormBlock)
+    register_part("block", "sandwich_norm", SandwichNormBlock)
     register_part("block", "hyper", HyperBlock)
 
 

@@ -32,6 +32,7 @@ class WeightSpec:
     optional: bool = False      # may be absent (the model says what stands in for it)
     floating: bool = True       # floating-point tensors; False for integer tables
     free_size: int = 0          # what random initialisation takes for a size of None
+    int_range: int = 0          # an integer table's entries lie in [0, int_range) and differ within a row (random initialisation)
 
     def fits(self, shape) -> bool:
         return len(shape) == len(self.shape) and all(w is None or w == g for w, g in zip(self.shape, shape))

@@ -63,7 +63,12 @@ def random_weights(manifest: Sequence[WeightSpec], seed: int, *, is_norm: Callab
         n = int(np.prod(shape))
         z = normal(w.name, seed, n).reshape(shape)
         kind = is_norm(w.name)
-        if kind == "identity":          # a square mixing matrix: the identity plus noise
+        if not w.floating:              # an integer table: every row the first entries of a permutation of [0, int_range)
+            if len(shape) != 2 or not 0 < shape[1] <= w.int_range:
+                raise ValueError(f"{w.name}: a random integer table needs rows of at most int_range different entries")
+            zz = normal(w.name, seed, shape[0] * w.int_range).reshape(shape[0], w.int_range)
+            out[w.name] = torch.from_numpy(np.argsort(zz, axis=1, kind="stable")[:, :shape[1]].astype(np.int32))
+        elif kind == "identity":          # a square mixing matrix: the identity plus noise
             out[w.name] = torch.from_numpy((np.eye(shape[0]) + std * z).astype(np.float32)).to(norm_dtype)
         elif kind:
             out[w.name] = torch.from_numpy((1.0 + norm_noise * z).astype(np.float32)).to(norm_dtype)
