@@ -2,7 +2,7 @@
 """Decode and prefill throughput of the engine on one B200, as one JSON line.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--impl ours|reference]
-                    [--model 135M|360M|1.7B] [--workload decode|mixed|prefill8k|lupanex|siparax]
+                    [--model 135M|360M|1.7B] [--workload decode|mixed|prefill8k|lupanex|siparax|manatar|tinevik]
 
 The default run is SmolLM2-135M's sizes with random weights (N(0, 0.02), norm weights 1, seed 0) in
 bfloat16, a batch of 8 requests each decoding from its own 2,048-token random prompt, cache context
@@ -26,6 +26,10 @@ kind of kernel by kind of kernel, against each kind's own roofline (LUPANEX_SIZE
 gelu feed-forward) at two sets of layer sizes, random weights, beside a Lupanex model (its closest relative here: attention and
 the gated delta rule in the same order of layers, one residual stream) of the same width, depth and number of feed-forward
 weights: the same measurements as --workload lupanex (SIPARAX_SIZES below).
+--workload manatar: the Manatar design, with dense and with routed feed-forwards, beside Lupanex (MANATAR_SIZES below).
+--workload tinevik: the Tinevik design (gated linear attention, attention with capped and mixed scores and rotated values, windowed
+latent attention, experts chosen by a table) beside Manatar with routed feed-forwards at equal width, depth, heads and weights a
+token uses: the same measurements (TINEVIK_SIZES below).
 --workload prefill8k: one 8,192-token prompt, in one step and in portions of 2,048 through the scheduler.
 
 --impl reference builds nothing of this repository's engine: it runs the unmodified reference program
@@ -535,6 +539,12 @@ def kind_of(launch):
         return "delta"
     if launch.startswith("mlstm"):
         return "mlstm"
+    if launch.startswith("gla"):
+        return "gla"
+    if launch == "latent_expand_gate":
+        return "expand"
+    if launch in ("sandwich_step", "xielu", "mixed_attn_prepare", "embed_scaled"):
+        return "between"
     if launch in ("embed_hashed", "residual_norm_step", "glu_clamped", "diff_attn_prepare", "diff_attn_combine"):
         return "between"
     if launch in ("hyper_step", "rmsnorm_rows", "layernorm_rows", "act_mul", "latent_prepare", "latent_rotate_q", "head_gate", "qk_norm_store"):
@@ -768,6 +778,85 @@ def manatar_run(a, pk, clocks):
     return results
 
 
+# ---------------------------------------------------------------------------------------------------------------
+# --workload tinevik
+# ---------------------------------------------------------------------------------------------------------------
+
+# Tinevik beside Manatar with routed feed-forwards, the engine's closest design: both keep a recurrent matrix state in six of eight
+# layers (token-by-token kernels of the same shape), a paged cache in the other two, and routed experts whose products are the same
+# grouped tensor-core products.  Equal width, depth, heads and weights a token uses: Tinevik's experts are 8 of which a token uses 2,
+# each half as wide as Manatar's dense feed-forward would be (Manatar: a shared one half as wide and 2 of 8 a quarter as wide); its first
+# layer has the dense feed-forward, 1.5 times as wide (two matrices instead of three).  Of its two cache layers one is the attention
+# with capped, mixed scores and rotated values, the other the windowed latent attention.
+TINEVIK_SIZES = {
+    "w1024": dict(width=1024, ff=2816, heads=4, kv=2, dim=64, vdim=128, layers=8, kv_rank=128, q_rank=256, window=1024, a_rank=16),
+    "w2048": dict(width=2048, ff=8192, heads=8, kv=2, dim=128, vdim=128, layers=8, kv_rank=128, q_rank=512, window=1024, a_rank=16),
+}
+
+
+def tinevik_config(sz):
+    H, G, dk, dv = sz["heads"], sz["kv"], sz["dim"], sz["vdim"]
+    att = dict(heads=2 * H, kv_heads=G, dim=dk, vdim=dv, scale=dk ** -0.5, softcap=50.0, rot=dict(base=500000.0, dims=dk // 2, scaling=dict(factor=2.0)))
+    lat = dict(heads=2 * H, dim=dk, vdim=dv, kv_rank=sz["kv_rank"], q_rank=sz["q_rank"], scale=dk ** -0.5, mask=dict(size=sz["window"]))
+    mem = dict(heads=H, dim=dk, vdim=2 * dv, tau=16.0)
+    moe = dict(kind="moe", expert=dict(ff=sz["ff"] // 2, limit=7.0), router=dict(experts=MANATAR_EXPERTS, top=MANATAR_TOP))
+    kinds = {3: ("attention", att), 7: ("latent_attention", lat)}
+    layers = [dict(type=kinds.get(i % 8, ("gla", mem))[0], mixer=kinds.get(i % 8, ("gla", mem))[1],
+                   mlp=dict(kind="dense", ff=3 * sz["ff"] // 2) if i == 0 else moe) for i in range(sz["layers"])]
+    return dict(architecture="Tinevik", vocab=LUPANEX_VOCAB, width=sz["width"], norm=dict(eps=1e-6), embedding=dict(scale=sz["width"] ** 0.5),
+                logit_scale=1.0, layers=layers)
+
+
+def tinevik_work(sz, T):
+    """Algorithmic work of one T-token prompt, by kind of kernel: (flops, bytes)."""
+    W, L = sz["width"], sz["layers"]
+    H, G, dk, dv, rk, rq, win = sz["heads"], sz["kv"], sz["dim"], sz["vdim"], sz["kv_rank"], sz["q_rank"], sz["window"]
+    n_att = n_lat = L // 8
+    n_mem = L - n_att - n_lat
+    mv, AH = 2 * dv, 2 * H
+    mem_rows = 2 * H * dk + 2 * H * mv + sz["a_rank"]
+    att_rows = AH * dk + G * dk + G * dv
+    lat_in = rq + rk + AH * dv
+    e_ff = sz["ff"] // 2
+    seen = float(T) * (T + 1) / 2 if win >= T else float(T) * win - win * (win - 1) / 2.0        # (query, key) pairs inside the window
+    return {
+        "product": (2.0 * T * (n_mem * W * (mem_rows + H * mv) + n_att * W * (att_rows + AH * dv) + n_lat * (W * lat_in + rq * AH * rk + AH * dv * W)
+                               + 2 * W * (3 * sz["ff"] // 2)), 0.0),
+        "attention": (n_att * float(T) * (T + 1) * AH * (dk + dv) + n_lat * 2.0 * seen * AH * 2 * rk, 0.0),
+        "gla": (n_mem * 5.0 * T * H * dk * mv, n_mem * T * (4.0 * mem_rows + 4.0 * H * dk + 2 * 4.0 * H * mv + 2.0 * H * mv)),
+        "experts": ((L - 1) * 2.0 * T * MANATAR_TOP * 3 * W * e_ff, (L - 1) * MANATAR_EXPERTS * 3.0 * W * e_ff * 2),
+        "expand": (n_lat * 2.0 * T * AH * rk * dv, 0.0),
+        "between": (0.0, 3 * L * T * W * 14.0 + n_att * T * (4.0 * att_rows + 2.0 * att_rows) + n_lat * T * (4.0 * (rq + rk) + 2.0 * (rq + rk))),
+    }
+
+
+def tinevik_run(a, pk, clocks):
+    import torch
+    from vitna_anchor_b200.engine.loading import random_model_on_device
+    results = {}
+    for name, sz in TINEVIK_SIZES.items():
+        msz = MANATAR_SIZES[name]
+        row = {}
+        for which, cfg, work in (("tinevik", tinevik_config(sz), tinevik_work(sz, PREFILL_TOKENS)),
+                                 ("manatar_moe", manatar_config(msz, True), manatar_work(msz, PREFILL_TOKENS, True))):
+            model = random_model_on_device(cfg, 0)
+            if model.max_positions > CONTEXT:
+                model.max_positions = CONTEXT           # the design has no limit of its own; the run's cache has
+            pf = prefill_run(model, None, clocks, repeats=3)
+            dec = decode_run(model, a.batch, min(a.steps, 32), a.warmup, clocks, with_e2e=False)
+            flops = sum(f for f, _ in work.values())
+            row[which] = {"weights_mb": round(model.step_weight_bytes() / 1e6, 1),
+                          "prefill_2048": {"tokens_per_s": round(pf["value"]), "ms": round(pf["ms"], 3),
+                                           "frac_bf16": round(flops / (pf["ms"] * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)},
+                          f"decode_b{a.batch}": {"tokens_per_s": round(dec["value"]), "ms_per_step": round(dec["ms_per_step"], 4),
+                                                 "frac_hbm": round(dec["gbs"] / pk["hbm_gbs"], 4), "launches_per_step": dec["launches"] // min(a.steps, 32)},
+                          "prompt_by_kind": prompt_by_kind(model, work, pk)}
+            del model
+            torch.cuda.empty_cache()
+        results[name] = row
+    return results
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -776,9 +865,10 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--model", default="135M", choices=sorted(MODELS), help="layer sizes: SmolLM2-135M (the default), 360M or 1.7B")
-    ap.add_argument("--workload", default="decode", choices=["decode", "mixed", "prefill8k", "lupanex", "siparax", "manatar"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "mixed", "prefill8k", "lupanex", "siparax", "manatar", "tinevik"],
                     help="decode (the default line), mixed (32 requests, 512-token portions beside decodes), prefill8k, lupanex "
-                         "(the Lupanex design beside a Llama model of equal size), siparax and manatar (those designs beside Lupanex)")
+                         "(the Lupanex design beside a Llama model of equal size), siparax and manatar (those designs beside Lupanex), "
+                         "tinevik (that design beside Manatar with routed feed-forwards)")
     ap.add_argument("--no-points", action="store_true", help="skip the other batches, models and the prefill")
     ap.add_argument("--only-prefill", action="store_true", help="run the prefill measurement alone (for profiling)")
     ap.add_argument("--profile-region", default="", choices=["", "decode", "prefill"],
@@ -830,6 +920,15 @@ def main():
         print(json.dumps({"metric": "Manatar (dense and routed feed-forwards) beside Lupanex (one residual stream) at equal width, depth and "
                           f"weights a token uses: tokens/s of a 2,048-token prompt and of batch-{a.batch} decoding from 2,048-token prompts; "
                           "a prompt's time by kind of kernel against its roofline", "impl": "ours", "dtype": "bf16",
+                          "data": "synthetic: random weights drawn on the device, uniform-random token ids", "peaks": pk, "sizes": r,
+                          "clocks": clocks.summary()}))
+        return 0
+    if a.workload == "tinevik":
+        r = tinevik_run(a, pk, clocks)
+        clocks.stop()
+        print(json.dumps({"metric": "Tinevik beside Manatar with routed feed-forwards at equal width, depth, heads and weights a token uses: tokens/s "
+                          f"of a 2,048-token prompt and of batch-{a.batch} decoding from 2,048-token prompts; a prompt's time by kind of kernel "
+                          "against its roofline", "impl": "ours", "dtype": "bf16",
                           "data": "synthetic: random weights drawn on the device, uniform-random token ids", "peaks": pk, "sizes": r,
                           "clocks": clocks.summary()}))
         return 0

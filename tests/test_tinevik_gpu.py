@@ -470,6 +470,78 @@ def test_the_recurrence_alone_on_scattered_slots_and_single_tokens():
             assert np.abs(state.cpu().numpy().reshape(S.shape) - S).max() < 2e-5 * max(1.0, np.abs(S).max())
 
 
+def _mixed_attention_plain(q, keys, vals, pos, H, G, scale, cap, mix, vfreq):
+    """One query token (all heads) over its keys: q [H, hd], keys [n, G, hd], vals [n, G, vd] as they lie in the cache -> [H, vd]."""
+    z = np.stack([keys[:, h // (H // G)] @ q[h] for h in range(H)]) * scale               # [H, n]
+    if cap > 0:
+        z = cap * np.tanh(z / cap)
+    if mix is not None:
+        z = mix @ z
+    e = np.exp(z - z.max(axis=1, keepdims=True))
+    p = e / e.sum(axis=1, keepdims=True)
+    o = np.stack([p[h] @ vals[:, h // (H // G)] for h in range(H)])
+    if vfreq is not None:
+        o = PT.turn_halves(o[:, None, :], [pos], vfreq, sign=-1.0)[:, 0, :]
+    return o
+
+
+@pytest.mark.parametrize("H,G,hd,vd,ps,with_mix", [(4, 1, 64, 64, 8, True), (8, 2, 128, 128, 16, True), (6, 3, 64, 128, 16, False),
+                                                   (16, 4, 128, 64, 32, True), (3, 1, 64, 64, 8, True), (5, 5, 24, 40, 8, True)])
+def test_the_forms_of_the_mixed_attention_alone(H, G, hd, vd, ps, with_mix):
+    """The general kernel against the statement written out, on pages that lie anywhere; then the split-key form (both dtypes) and
+    the tensor-core form (bfloat16, where it takes the sizes) against the general kernel: a segment far into its context whose
+    queries cross a step of 64 keys and a run of 128, and one from its first token."""
+    from vitna_anchor_b200 import ops
+    rng = np.random.default_rng(H * 100 + hd)
+    ctx_len, q_lens = (300, 45), (70, 45)
+    n_pages = sum(-(-c // ps) for c in ctx_len) + 3
+    order = rng.permutation(n_pages)
+    max_blocks = max(-(-c // ps) for c in ctx_len)
+    bt = np.zeros((2, max_blocks), dtype=np.int32)
+    used = 0
+    for s_, c in enumerate(ctx_len):
+        nb = -(-c // ps)
+        bt[s_, :nb] = order[used:used + nb]
+        used += nb
+    T = sum(q_lens)
+    token_seg = np.concatenate([np.full(n, i, dtype=np.int32) for i, n in enumerate(q_lens)])
+    positions = np.concatenate([np.arange(c - n, c, dtype=np.int32) for c, n in zip(ctx_len, q_lens)])
+    mix = (np.eye(H) * 0.7 + rng.standard_normal((H, H)) * 0.4) if with_mix else None
+    vfreq = PT.frequencies(300.0, vd)
+    scale, cap = 2.0 * hd ** -0.5, 3.0
+    pages0 = rng.standard_normal((n_pages, ps * G * (hd + vd)))
+    q0 = rng.standard_normal((T, H * hd))
+    dev_i = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    outs = {}
+    for dtype in (torch.float32, torch.bfloat16):
+        pages, q = _dev(pages0, dtype), _dev(q0, dtype)
+        args = (H, G, hd, vd, ps, scale, cap, None if mix is None else _dev(mix), _dev(vfreq))
+        rows = ops.attention_mixed_rows(q, pages, dev_i(bt), dev_i(token_seg), dev_i(positions), torch.empty(T, H * vd, dtype=dtype, device="cuda"), *args)
+        ref = rows.float().cpu().numpy()
+        if dtype == torch.float32:      # the general kernel against the statement, on a few tokens
+            pg = pages0.astype(np.float32).astype(np.float64)
+            for t in (0, 33, 69, 70, 71, T - 1):
+                sg, pos = token_seg[t], positions[t]
+                keys = np.stack([pg[bt[sg, j // ps]][:ps * G * hd].reshape(G, ps, hd)[:, j % ps] for j in range(pos + 1)])
+                vals = np.stack([pg[bt[sg, j // ps]][ps * G * hd:].reshape(G, ps, vd)[:, j % ps] for j in range(pos + 1)])
+                want = _mixed_attention_plain(q0[t].astype(np.float32).astype(np.float64).reshape(H, hd), keys, vals, pos, H, G, scale, cap, mix, vfreq)
+                assert np.abs(ref[t].reshape(H, vd) - want).max() < 2e-5 * max(1.0, np.abs(want).max()), t
+        toks = np.array([0, 5, 69, 70, 100, T - 1], dtype=np.int32)
+        for nsplit, per in ((3, 1), (2, 2), (40, 1)):
+            part = torch.empty(len(toks) * nsplit * H * (vd + 2), device="cuda")
+            got = torch.zeros(T, H * vd, dtype=dtype, device="cuda")
+            ops.attention_mixed_split(q, pages, dev_i(bt), dev_i(token_seg), dev_i(positions), got, part, nsplit, per, *args, 0, dev_i(toks))
+            tol = 2e-5 if dtype == torch.float32 else 1.5e-2
+            assert np.abs(got.float().cpu().numpy()[toks] - ref[toks]).max() < tol * max(1.0, np.abs(ref).max()), (dtype, nsplit)
+        if dtype == torch.bfloat16 and hd in ops.MIXED_PREFILL_SIZES and vd in ops.MIXED_PREFILL_SIZES:
+            tiles = np.array([[0, 64, 230, 0], [64, 6, 294, 0], [70, 45, 0, 1]], dtype=np.int32)
+            got = torch.zeros(T, H * vd, dtype=dtype, device="cuda")
+            ops.attention_mixed_prefill(q, pages, dev_i(bt), dev_i(tiles), got, *args)
+            torch.cuda.synchronize()
+            d = np.abs(got.float().cpu().numpy() - ref)
+            assert d.max() < 2e-2 * max(1.0, np.abs(ref).max()), (d.max(), np.unravel_index(d.argmax(), d.shape))
+
+
 def test_the_values_expansion_with_its_gate_and_the_experts_table():
     from vitna_anchor_b200 import ops
     rng = np.random.default_rng(13)

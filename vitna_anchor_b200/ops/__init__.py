@@ -1611,12 +1611,89 @@ def attention_mixed_rows(q: torch.Tensor, cache_layer: torch.Tensor, block_table
     return out
 
 
+MIXED_PREFILL_SIZES = (64, 128)
+MIXED_SPLIT_MAX = 64            # most splits of a decoded token's keys
+
+
+def attention_mixed_split_plan(max_context: int):
+    """(splits, runs of 128 keys a split) for contexts of up to max_context positions: as many splits as there are runs, up to
+    MIXED_SPLIT_MAX.  It depends on the engine's limit alone, so a captured graph holds for every batch."""
+    runs = max(1, -(-max_context // 128))
+    per = -(-runs // MIXED_SPLIT_MAX)
+    return -(-runs // per), per
+
+
+def attention_mixed_split(q: torch.Tensor, cache_layer: torch.Tensor, block_tables: torch.Tensor, token_seg: torch.Tensor, positions: torch.Tensor,
+                          out: torch.Tensor, part: torch.Tensor, nsplit: int, runs_per_split: int, nh: int, nkv: int, hd: int, vd: int,
+                          page_size: int, scale: float, cap: float = 0.0, mix: Optional[torch.Tensor] = None, vfreq: Optional[torch.Tensor] = None,
+                          window: int = 0, tok_list: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """attention_mixed_rows for single decoded tokens, a block a (token, split of the keys) and a launch that adds the splits up;
+    part: float32 scratch of tokens * nsplit * nh * (vd + 2) values."""
+    _req(q, "q", dims=2); _req(cache_layer, "cache_layer", q.dtype); _req(block_tables, "block_tables", torch.int32, 2)
+    _req(token_seg, "token_seg", torch.int32, 1); _req(positions, "positions", torch.int32, 1); _req(out, "out", q.dtype, 2)
+    _req(part, "part", torch.float32, 1)
+    T = q.shape[0]
+    n = T if tok_list is None else tok_list.shape[0]
+    if q.shape[1] != nh * hd or out.shape != (T, nh * vd) or _page_size_of(cache_layer, nkv, hd, vd) != page_size:
+        raise KernelError("attention_mixed_split: shapes do not fit the head counts")
+    if part.numel() < n * nsplit * nh * (vd + 2):
+        raise KernelError("attention_mixed_split: the scratch is too small")
+    if (mix is not None and mix.shape != (nh, nh)) or (vfreq is not None and vfreq.shape[0] != vd // 2):
+        raise KernelError("attention_mixed_split: the mixing matrix or the values' frequencies do not fit")
+    if tok_list is not None:
+        _req(tok_list, "tok_list", torch.int32, 1)
+    _check(lib().vk_attention_mixed_split(_p(q), _p(cache_layer), _p(block_tables), _p(token_seg), _p(positions), _p(tok_list), _p(out), _p(part), n,
+                                          nsplit, runs_per_split, nh, nkv, hd, vd, page_size, block_tables.shape[1], ctypes.c_float(scale),
+                                          ctypes.c_float(cap), _p(mix), _p(vfreq), window, _dt(q), _stream()), "attention_mixed_split")
+    add_launches(1)
+    return out
+
+
+def attention_mixed_prefill(q: torch.Tensor, cache_layer: torch.Tensor, block_tables: torch.Tensor, tiles: torch.Tensor, out: torch.Tensor, nh: int,
+                            nkv: int, hd: int, vd: int, page_size: int, scale: float, cap: float = 0.0, mix: Optional[torch.Tensor] = None,
+                            vfreq: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The same attention for the tokens of prompt portions on the tensor cores (bfloat16): tiles int32 [n, 4] = first token, rows (up to
+    64), position of the first token, segment.  Up to 16 heads; key and value sizes of MIXED_PREFILL_SIZES; no window."""
+    _req(q, "q", torch.bfloat16, 2); _req(cache_layer, "cache_layer", torch.bfloat16); _req(block_tables, "block_tables", torch.int32, 2)
+    _req(tiles, "tiles", torch.int32, 2); _req(out, "out", torch.bfloat16, 2)
+    T = q.shape[0]
+    if q.shape[1] != nh * hd or out.shape != (T, nh * vd) or tiles.shape[1] != 4 or _page_size_of(cache_layer, nkv, hd, vd) != page_size:
+        raise KernelError("attention_mixed_prefill: shapes do not fit the head counts")
+    if (mix is not None and mix.shape != (nh, nh)) or (vfreq is not None and vfreq.shape[0] != vd // 2):
+        raise KernelError("attention_mixed_prefill: the mixing matrix or the values' frequencies do not fit")
+    _check(lib().vk_attention_mixed_prefill(_p(q), _p(cache_layer), _p(block_tables), _p(tiles), _p(out), tiles.shape[0], nh, nkv, hd, vd, page_size,
+                                            block_tables.shape[1], ctypes.c_float(scale), ctypes.c_float(cap), _p(mix), _p(vfreq), _stream()),
+           "attention_mixed_prefill")
+    return out
+
+
 def attention_mixed(q: torch.Tensor, pages: torch.Tensor, meta, ctx, out: torch.Tensor, nh: int, nkv: int, hd: int, vd: int, page_size: int,
                     scale: float, cap: float = 0.0, mix: Optional[torch.Tensor] = None, vfreq: Optional[torch.Tensor] = None,
                     window: int = 0) -> torch.Tensor:
-    """The attention with capped, mixed scores of a mixed batch over the paged cache; `meta` is the page group's GroupMeta."""
-    return attention_mixed_rows(q, pages, meta.block_tables, ctx.token_seg, ctx.positions, out, nh, nkv, hd, vd, page_size, scale, cap, mix,
-                                vfreq, window)
+    """The attention with capped, mixed scores of a mixed batch over the paged cache; `meta` is the page group's GroupMeta.  Single
+    decoded tokens take the split-key form, tokens of prompt portions the tensor-core kernel (bfloat16, sizes it is built for);
+    whatever is left, and the whole exact 32-bit routing, takes attention_mixed_rows, which takes every size."""
+    exact = q.dtype == torch.float32 and _float32_exact
+    ws = ctx.workspace
+    dec_ok = bool(ctx.num_dec) and not exact and nh * vd <= 4096
+    pre_ok = (bool(ctx.num_pre) and q.dtype == torch.bfloat16 and hd in MIXED_PREFILL_SIZES and vd in MIXED_PREFILL_SIZES and nh <= 16
+              and window == 0 and ctx.pre_tiles is not None and q.data_ptr() % 16 == 0 and pages.data_ptr() % 16 == 0)
+    rows = lambda toks: attention_mixed_rows(q, pages, meta.block_tables, ctx.token_seg, ctx.positions, out, nh, nkv, hd, vd, page_size, scale, cap,
+                                             mix, vfreq, window, toks)
+    if dec_ok:
+        nsplit, per = attention_mixed_split_plan(ws.max_context)
+        part = ws.flat(f"matt.part/{nh}/{vd}/{nsplit}", ws.max_segments * nsplit * nh * (vd + 2), torch.float32)
+        attention_mixed_split(q, pages, meta.block_tables, ctx.token_seg, ctx.positions, out, part, nsplit, per, nh, nkv, hd, vd, page_size, scale,
+                              cap, mix, vfreq, window, ctx.dec_tokens)
+    if pre_ok:
+        attention_mixed_prefill(q, pages, meta.block_tables, ctx.pre_tiles, out, nh, nkv, hd, vd, page_size, scale, cap, mix, vfreq)
+    if not dec_ok and not pre_ok:
+        return rows(None)
+    if ctx.num_pre and not pre_ok:
+        rows(ctx.pre_tokens)
+    if ctx.num_dec and not dec_ok:
+        rows(ctx.dec_tokens)
+    return out
 
 
 def latent_expand_gate(lat: torch.Tensor, w: torch.Tensor, gates: Optional[torch.Tensor], gate_off: int, H: int, rank: int, vd: int,
