@@ -318,7 +318,8 @@ __global__ void __launch_bounds__(AM_THREADS) attention_mixed_combine_kernel(con
 // into shared memory; after a barrier every warp reads, for its own fragment's places, the scores of all heads and mixes them
 // (float32), masks, and carries the running maximum and sum of its 16 rows in registers; the weights leave as two bfloat16
 // parts (high and low, so that the product with the values keeps float32 weights' accuracy) and O += P V runs on the tensor
-// cores against the values, which were transposed on their way into shared memory.  At the end a thread turns its pairs
+// cores against the values, which lie in shared memory a key a row and are read with transposing loads.  Keys and values of a
+// step come by cp.async into one of two stages, the next step's while this step's are worked on.  At the end a thread turns its pairs
 // (d, d + vd / 2) back by the query's position: both lie in its own fragment.
 // ---------------------------------------------------------------------------------------------------------------
 
@@ -348,16 +349,28 @@ __device__ __forceinline__ void split_bf16(float x, float y, uint32_t& hi, uint3
     lo = *reinterpret_cast<uint32_t*>(&l2);
 }
 
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void* p) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], const void* p) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void mp_cp16(void* dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+
 template <int HD, int VD, int MAXT>       // MAXT: the most threads of a block (32 a head): up to 8 heads leave a thread 255 registers
 __global__ void __launch_bounds__(MAXT) attention_mixed_prefill_kernel(
     const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ cache, const int32_t* __restrict__ block_tables,
     const int32_t* __restrict__ tiles, __nv_bfloat16* __restrict__ out, int nh, int nkv, int page_size, int max_blocks, float scale, float cap,
-    const float* __restrict__ mix, const float* __restrict__ vfreq) {
-    constexpr int KT = HD / 16, NT = VD / 8, KP = HD + 8, VP = MP_KEYS + 8;
+    const float* __restrict__ mix, const float* __restrict__ vfreq, int stages) {
+    constexpr int KT = HD / 16, NT = VD / 8, KP = HD + 8, VP = VD + 8;
     extern __shared__ __align__(16) unsigned char mp_sh[];
-    __nv_bfloat16* Ks = reinterpret_cast<__nv_bfloat16*>(mp_sh);                       // [nkv][64][KP]
-    __nv_bfloat16* Vt = Ks + (size_t)nkv * MP_KEYS * KP;                               // [nkv][VD][VP]: values transposed
-    float* raw = reinterpret_cast<float*>(Vt + (size_t)nkv * VD * VP);                 // [nh][16][MP_RAW] capped scores
+    const size_t stage_elems = (size_t)nkv * MP_KEYS * (KP + VP);                      // a stage: keys [nkv][64][KP], then values [nkv][64][VP]
+    __nv_bfloat16* st0 = reinterpret_cast<__nv_bfloat16*>(mp_sh);
+    float* raw = reinterpret_cast<float*>(st0 + (size_t)stages * stage_elems);         // [nh][16][MP_RAW] capped scores
     float* mx = raw + (size_t)nh * MP_ROWS * MP_RAW;                                   // [nh][nh]
     const int tid = threadIdx.x, lane = tid & 31, h = tid >> 5, gid = lane >> 2, tig = lane & 3;
     const int tile = blockIdx.x >> 2, sub = blockIdx.x & 3;
@@ -389,38 +402,59 @@ __global__ void __launch_bounds__(MAXT) attention_mixed_prefill_kernel(
     const int pos_hi = pos0 + rows - 1;
     const int qpos[2] = {pos0 + gid, pos0 + gid + 8};
 
-    for (int ks = 0; ks <= pos_hi; ks += MP_KEYS) {
-        // the step's keys as they lie, its values transposed; keys beyond the tile's last position are zeros
+    // a step's keys and values go from the pages into a stage as they lie (cp.async, 16 bytes a piece); keys beyond the tile's last
+    // position are zeros.  With two stages the next step's rows are on their way while this step's are worked on.
+    auto issue = [&](int stage, int ks) {
+        __nv_bfloat16* Ks = st0 + (size_t)stage * stage_elems;
+        __nv_bfloat16* Vs = Ks + (size_t)nkv * MP_KEYS * KP;
         for (int i = tid; i < nkv * MP_KEYS * (HD / 8); i += blockDim.x) {
             const int c = i % (HD / 8), kk = (i / (HD / 8)) % MP_KEYS, gg = i / ((HD / 8) * MP_KEYS);
             const int key = ks + kk;
-            uint4 v = make_uint4(0u, 0u, 0u, 0u);
+            __nv_bfloat16* dst = Ks + ((size_t)gg * MP_KEYS + kk) * KP + c * 8;
             if (key <= pos_hi)
-                v = *reinterpret_cast<const uint4*>(cache + (size_t)bt[key / page_size] * page_stride + ((size_t)gg * page_size + key % page_size) * HD + c * 8);
-            *reinterpret_cast<uint4*>(Ks + ((size_t)gg * MP_KEYS + kk) * KP + c * 8) = v;
+                mp_cp16(dst, cache + (size_t)bt[key / page_size] * page_stride + ((size_t)gg * page_size + key % page_size) * HD + c * 8);
+            else
+                *reinterpret_cast<uint4*>(dst) = make_uint4(0u, 0u, 0u, 0u);
         }
         for (int i = tid; i < nkv * MP_KEYS * (VD / 8); i += blockDim.x) {
-            const int kk = i % MP_KEYS, c = (i / MP_KEYS) % (VD / 8), gg = i / (MP_KEYS * (VD / 8));
+            const int c = i % (VD / 8), kk = (i / (VD / 8)) % MP_KEYS, gg = i / ((VD / 8) * MP_KEYS);
             const int key = ks + kk;
-            uint4 v = make_uint4(0u, 0u, 0u, 0u);
+            __nv_bfloat16* dst = Vs + ((size_t)gg * MP_KEYS + kk) * VP + c * 8;
             if (key <= pos_hi)
-                v = *reinterpret_cast<const uint4*>(cache + (size_t)bt[key / page_size] * page_stride + v_base + ((size_t)gg * page_size + key % page_size) * VD + c * 8);
-            const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&v);
-            __nv_bfloat16* dst = Vt + ((size_t)gg * VD + c * 8) * VP + kk;
-#pragma unroll
-            for (int j = 0; j < 8; j++) dst[(size_t)j * VP] = e[j];
+                mp_cp16(dst, cache + (size_t)bt[key / page_size] * page_stride + v_base + ((size_t)gg * page_size + key % page_size) * VD + c * 8);
+            else
+                *reinterpret_cast<uint4*>(dst) = make_uint4(0u, 0u, 0u, 0u);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    issue(0, 0);
+    int step = 0;
+    for (int ks = 0; ks <= pos_hi; ks += MP_KEYS, step++) {
+        const int stage = stages > 1 ? (step & 1) : 0;
+        if (stages > 1 && ks + MP_KEYS <= pos_hi) {
+            issue(stage ^ 1, ks + MP_KEYS);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            if (stages == 1 && step > 0) issue(0, ks);                      // one stage: the barrier at the loop's end freed it
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
         }
         __syncthreads();
+        const __nv_bfloat16* Ks = st0 + (size_t)stage * stage_elems;
+        const __nv_bfloat16* Vs = Ks + (size_t)nkv * MP_KEYS * KP;
         float s[MP_KEYS / 8][4];
 #pragma unroll
         for (int nt = 0; nt < MP_KEYS / 8; nt++) { s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.0f; }
         const __nv_bfloat16* kg = Ks + (size_t)g * MP_KEYS * KP;
+        // four 8 x 8 pieces a load: keys 8 nt .. and 8 (nt + 1) .., each with columns 16 kt .. + 7 and + 8 .. + 15
+        const __nv_bfloat16* k_lane = kg + (size_t)((lane >> 4) * 8 + (lane & 7)) * KP + ((lane >> 3) & 1) * 8;
 #pragma unroll
         for (int kt = 0; kt < KT; kt++) {
 #pragma unroll
-            for (int nt = 0; nt < MP_KEYS / 8; nt++) {
-                const __nv_bfloat16* kr = kg + (size_t)(nt * 8 + gid) * KP + kt * 16 + 2 * tig;
-                mma_bf16_16816(s[nt], qa[kt], *reinterpret_cast<const uint32_t*>(kr), *reinterpret_cast<const uint32_t*>(kr + 8));
+            for (int nt = 0; nt < MP_KEYS / 8; nt += 2) {
+                uint32_t b[4];
+                ldsm_x4(b, k_lane + (size_t)nt * 8 * KP + kt * 16);
+                mma_bf16_16816(s[nt], qa[kt], b[0], b[1]);
+                mma_bf16_16816(s[nt + 1], qa[kt], b[2], b[3]);
             }
         }
         float* mine = raw + (size_t)h * MP_ROWS * MP_RAW;
@@ -488,7 +522,8 @@ __global__ void __launch_bounds__(MAXT) attention_mixed_prefill_kernel(
         }
 #pragma unroll
         for (int nt = 0; nt < NT; nt++) { o[nt][0] *= corr[0]; o[nt][1] *= corr[0]; o[nt][2] *= corr[1]; o[nt][3] *= corr[1]; }
-        const __nv_bfloat16* vg = Vt + (size_t)g * VD * VP;
+        // the values lie a key a row: the transposing load gives keys 16 kt .. + 7 and + 8 .. + 15 of columns 8 nt .. and 8 (nt + 1) ..
+        const __nv_bfloat16* v_lane = Vs + ((size_t)g * MP_KEYS + (lane & 15)) * VP + (lane >> 4) * 8;
 #pragma unroll
         for (int kt = 0; kt < MP_KEYS / 16; kt++) {
             uint32_t hi[4], lo[4];
@@ -497,11 +532,13 @@ __global__ void __launch_bounds__(MAXT) attention_mixed_prefill_kernel(
             split_bf16(s[2 * kt + 1][0], s[2 * kt + 1][1], hi[2], lo[2]);
             split_bf16(s[2 * kt + 1][2], s[2 * kt + 1][3], hi[3], lo[3]);
 #pragma unroll
-            for (int nt = 0; nt < NT; nt++) {
-                const __nv_bfloat16* vr = vg + (size_t)(nt * 8 + gid) * VP + kt * 16 + 2 * tig;
-                const uint32_t b0 = *reinterpret_cast<const uint32_t*>(vr), b1 = *reinterpret_cast<const uint32_t*>(vr + 8);
-                mma_bf16_16816(o[nt], hi, b0, b1);
-                mma_bf16_16816(o[nt], lo, b0, b1);
+            for (int nt = 0; nt < NT; nt += 2) {
+                uint32_t b[4];
+                ldsm_x4_trans(b, v_lane + (size_t)kt * 16 * VP + nt * 8);
+                mma_bf16_16816(o[nt], hi, b[0], b[1]);
+                mma_bf16_16816(o[nt], lo, b[0], b[1]);
+                mma_bf16_16816(o[nt + 1], hi, b[2], b[3]);
+                mma_bf16_16816(o[nt + 1], lo, b[2], b[3]);
             }
         }
         __syncthreads();                                                    // the step's arrays are filled again
@@ -644,7 +681,9 @@ VK_API int vk_attention_mixed_prefill(const void* q, const void* cache, const in
     if (nh <= 0 || nkv <= 0 || nh % nkv != 0 || page_size <= 0 || max_blocks <= 0) return VK_BAD_SHAPE;
     if (nh > 16 || !((hd == 64 || hd == 128) && (vd == 64 || vd == 128))) return VK_BAD_SHAPE;
     if (((uintptr_t)q % 16) || ((uintptr_t)cache % 16) || ((uintptr_t)out % 4)) return VK_BAD_ALIGNMENT;
-    const size_t smem = (size_t)nkv * MP_KEYS * (hd + 8) * 2 + (size_t)nkv * vd * (MP_KEYS + 8) * 2 + (size_t)nh * MP_ROWS * MP_RAW * 4 + (size_t)nh * nh * 4;
+    const size_t stage = (size_t)nkv * MP_KEYS * (hd + 8 + vd + 8) * 2, rest = (size_t)nh * MP_ROWS * MP_RAW * 4 + (size_t)nh * nh * 4;
+    const int stages = 2 * stage + rest <= 220 * 1024 ? 2 : 1;
+    const size_t smem = stages * stage + rest;
     if (smem > 220 * 1024) return VK_TOO_LARGE;
 #define VK_MP(HDV, VDV)                                                                                                                       \
     do {                                                                                                                                      \
@@ -652,7 +691,7 @@ VK_API int vk_attention_mixed_prefill(const void* q, const void* cache, const in
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                                   \
         if (e != cudaSuccess) return (int)e;                                                                                                  \
         kern<<<n_tiles * 4, nh * 32, smem, stream>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, block_tables, tiles, (__nv_bfloat16*)out, nh, \
-                                                     nkv, page_size, max_blocks, scale, cap, mix, vfreq);                                     \
+                                                     nkv, page_size, max_blocks, scale, cap, mix, vfreq, stages);                             \
         return launch_status();                                                                                                               \
     } while (0)
     if (hd == 64 && vd == 64) VK_MP(64, 64);

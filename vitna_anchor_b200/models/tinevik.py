@@ -18,6 +18,7 @@ import numpy as np
 import torch
 
 from ..config.tinevik import DenseFFSpec, GlaSpec, MixedAttentionSpec, TableExpertsSpec, TinevikConfig, WindowLatentSpec
+from ..parts.block import SandwichFlush
 from ..parts.embedding import LMHead, ScaledEmbedding
 from ..parts.registry import make_part
 from ..weights.loader import WeightSpec
@@ -146,4 +147,4 @@ def build_tinevik(cfg: TinevikConfig, weights: Dict[str, torch.Tensor], dtype: t
     # logits = c * E LN(x): the factor rides on the last norm's weight and bias, so the output product is the plain one
     return DecoderModel(embedding=embedding, blocks=blocks, schedule=schedule, final_norm=norm("final.norm", cfg.logit_scale),
                         lm_head=LMHead(cfg.vocab, W, embedding.table), position=None, dtype=dtype, vocab_size=cfg.vocab,
-                        max_positions=UNBOUNDED_POSITIONS, config=cfg)
+                        max_positions=UNBOUNDED_POSITIONS, config=cfg, collect=SandwichFlush(cfg.eps))

@@ -15,7 +15,7 @@ import torch
 from .. import ops
 
 from ..cache.manager import LayerCacheView
-from .base import Block, FeedForward, Mixer, Norm, StepContext
+from .base import Block, FeedForward, Mixer, Norm, Part, StepContext
 
 
 class PreNormBlock(Block):
@@ -85,8 +85,11 @@ class SandwichNormBlock(Block):
 
     The sublayers keep the framework's contract (they ADD their result into a float32 buffer): the buffer is a zeroed row y, and ONE
     kernel between two sublayers norms y, sums it into the float32 residual row, zeroes y again and norms the new row for the next
-    sublayer.  The first kernel of a block only zeroes y and norms x; the last only sums (the next block's pre-norm may belong to
-    another kind of block)."""
+    sublayer.  A block leaves its last sum pending for the next block's first kernel (two launches a layer instead of three); behind
+    the last block SandwichFlush, the decoder's `collect` part, does what is left.  While something looks at the residual rows
+    between the runs of the schedule (ctx.after_run), every block finishes its own sum."""
+
+    PENDING = "sandwich.pending"
 
     def __init__(self, mixer_norm: Norm, mixer_post: Norm, mixer: Mixer, ffn_norm: Optional[Norm] = None, ffn_post: Optional[Norm] = None,
                  ffn: Optional[FeedForward] = None):
@@ -100,17 +103,44 @@ class SandwichNormBlock(Block):
     def tensors(self):
         return [t for p in (self.mixer_norm, self.mixer_post, self.mixer, self.ffn_norm, self.ffn_post, self.ffn) if p is not None for t in p.tensors()]
 
+    @staticmethod
+    def buffer(x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        T, W, ws = ctx.num_tokens, x.shape[1], ctx.workspace
+        return ws.flat(f"sandwich.y/{W}", ws.max_tokens * W, torch.float32, zero=True)[:T * W].view(T, W)
+
+    @classmethod
+    def take_pending(cls, ctx: StepContext):
+        """The (weight, bias) of a sum that the block before left to do, if it did so in this pass."""
+        left = ctx.extra.pop(cls.PENDING, None)
+        return left[1] if left is not None and left[0] == ctx.extra.get("pass", 0) else None
+
     def forward(self, x: torch.Tensor, ctx: StepContext, cache: Optional[LayerCacheView], write_cache: bool = True) -> None:
         T, W, ws = ctx.num_tokens, x.shape[1], ctx.workspace
-        y = ws.flat(f"sandwich.y/{W}", ws.max_tokens * W, torch.float32, zero=True)[:T * W].view(T, W)
+        y = self.buffer(x, ctx)
         xn = ws.rows("block.xn", T, W, ctx.dtype)
         pair = lambda n: (n.weight, n.bias)
         eps = self.mixer_norm.eps
-        ops.sandwich_step(x, y, None, pair(self.mixer_norm), xn, eps)
+        ops.sandwich_step(x, y, self.take_pending(ctx), pair(self.mixer_norm), xn, eps)
         self.mixer.forward(xn, ctx, cache, y, write_cache)
-        if self.ffn is None:
-            ops.sandwich_step(x, y, pair(self.mixer_post), None, None, eps)
-            return
-        ops.sandwich_step(x, y, pair(self.mixer_post), pair(self.ffn_norm), xn, eps)
-        self.ffn.forward(xn, ctx, y)
-        ops.sandwich_step(x, y, pair(self.ffn_post), None, None, eps)
+        last = self.mixer_post
+        if self.ffn is not None:
+            ops.sandwich_step(x, y, pair(self.mixer_post), pair(self.ffn_norm), xn, eps)
+            self.ffn.forward(xn, ctx, y)
+            last = self.ffn_post
+        if ctx.after_run is not None:
+            ops.sandwich_step(x, y, pair(last), None, None, eps)
+        else:
+            ctx.extra[self.PENDING] = (ctx.extra.get("pass", 0), pair(last))
+
+
+class SandwichFlush(Part):
+    """Behind the last SandwichNormBlock: the sum that it left pending.  Used as a decoder's `collect` part."""
+
+    def __init__(self, eps: float):
+        self.eps = float(eps)
+
+    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        post = SandwichNormBlock.take_pending(ctx)
+        if post is not None:
+            ops.sandwich_step(x, SandwichNormBlock.buffer(x, ctx), post, None, None, self.eps)
+        return x
