@@ -361,6 +361,19 @@ __device__ __forceinline__ void mp_cp16(void* dst, const void* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
 }
 
+// For the bfloat16 tensor-core kernel alone: e^x and tanh(x) through ex2.approx (two units in the last place of a float32) and a fast
+// division.  tanh(x) = 1 - 2 / (e^(2x) + 1) is off by about 1e-7 in absolute terms, which the cap's factor turns into a score's error of
+// 1e-5 at most, a thousandth of what the bfloat16 queries and keys leave.  The general kernel keeps tanhf and expf.
+__device__ __forceinline__ float mp_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ float mp_tanh(float x) {
+    const float t = mp_exp2(fminf(x, 20.0f) * 2.8853900817779268f);       // e^(2x), the argument bounded so that t stays finite
+    return 1.0f - __fdividef(2.0f, t + 1.0f);
+}
+
 template <int HD, int VD, int MAXT>       // MAXT: the most threads of a block (32 a head): up to 8 heads leave a thread 255 registers
 __global__ void __launch_bounds__(MAXT) attention_mixed_prefill_kernel(
     const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ cache, const int32_t* __restrict__ block_tables,
@@ -401,6 +414,8 @@ __global__ void __launch_bounds__(MAXT) attention_mixed_prefill_kernel(
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
     const int pos_hi = pos0 + rows - 1;
     const int qpos[2] = {pos0 + gid, pos0 + gid + 8};
+    const float inv_cap = cap > 0.0f ? 1.0f / cap : 0.0f;
+    constexpr float LOG2E = 1.4426950408889634f;
 
     // a step's keys and values go from the pages into a stage as they lie (cp.async, 16 bytes a piece); keys beyond the tile's last
     // position are zeros.  With two stages the next step's rows are on their way while this step's are worked on.
@@ -463,7 +478,7 @@ __global__ void __launch_bounds__(MAXT) attention_mixed_prefill_kernel(
 #pragma unroll
             for (int e = 0; e < 4; e++) {
                 float z = s[nt][e] * scale;
-                if (cap > 0.0f) z = cap * tanhf(z / cap);
+                if (cap > 0.0f) z = cap * mp_tanh(z * inv_cap);
                 s[nt][e] = z;
             }
             if (mix) {
@@ -507,7 +522,7 @@ __global__ void __launch_bounds__(MAXT) attention_mixed_prefill_kernel(
             rmax[r] = fmaxf(rmax[r], __shfl_xor_sync(0xffffffffu, rmax[r], 2));
             const float m_new = fmaxf(m_run[r], rmax[r]);
             m_use[r] = m_new == -INFINITY ? 0.0f : m_new;                   // a row of the tile that no token has
-            corr[r] = expf(m_run[r] - m_use[r]);                            // 0 while nothing has been seen
+            corr[r] = mp_exp2((m_run[r] - m_use[r]) * LOG2E);               // 0 while nothing has been seen
             m_run[r] = m_new;
             l_run[r] *= corr[r];
         }
@@ -515,7 +530,7 @@ __global__ void __launch_bounds__(MAXT) attention_mixed_prefill_kernel(
         for (int nt = 0; nt < MP_KEYS / 8; nt++) {
 #pragma unroll
             for (int e = 0; e < 4; e++) {
-                const float pv = expf(s[nt][e] - m_use[e >> 1]);            // e^(-inf) = 0 for what the mask took
+                const float pv = mp_exp2((s[nt][e] - m_use[e >> 1]) * LOG2E);   // 2^(-inf) = 0 for what the mask took
                 s[nt][e] = pv;
                 l_run[e >> 1] += pv;
             }

@@ -90,15 +90,106 @@ __global__ void __launch_bounds__(256) residual_norm_step_kernel(float* __restri
 // registers (up to SW_KEEP a thread) between the sums, which meet in an order that depends on the width alone.
 constexpr int SW_THREADS = 128;
 constexpr int SW_KEEP = 16;
+
+template <typename T> __device__ __forceinline__ void sw_store4(T* p, float a, float b, float c, float d);
+template <> __device__ __forceinline__ void sw_store4<float>(float* p, float a, float b, float c, float d) {
+    *reinterpret_cast<float4*>(p) = make_float4(a, b, c, d);
+}
+template <> __device__ __forceinline__ void sw_store4<__nv_bfloat16>(__nv_bfloat16* p, float a, float b, float c, float d) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+    uint2 v;
+    v.x = *reinterpret_cast<uint32_t*>(&lo);
+    v.y = *reinterpret_cast<uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(p) = v;
+}
+
+// Rows whose width is a multiple of four, of up to 4 * SW_THREADS * SW_VEC values, with every pointer on 16 bytes: all of a thread's
+// 16-byte pieces of y and x are asked for before any is used, and stay in registers.  The sums meet in the order of the scalar form's
+// block_sum; a thread's own partial sums run over other elements, so the two forms agree to rounding, and which form a row takes
+// depends on the width and the buffers alone, never on the batch.
+constexpr int SW_VEC = 4;
+template <typename T>
+__device__ __forceinline__ void sandwich_row_vec(float* __restrict__ x, float* __restrict__ y, const float* __restrict__ wp, const float* __restrict__ bp,
+                                                 const float* __restrict__ wn, const float* __restrict__ bn, T* __restrict__ xn, int n, float eps,
+                                                 float* scratch) {
+    const int tid = threadIdx.x;
+    float4 v[SW_VEC], u[SW_VEC];
+#pragma unroll
+    for (int j = 0; j < SW_VEC; j++) {
+        const int i = (tid + j * SW_THREADS) * 4;
+        u[j] = i < n ? *reinterpret_cast<const float4*>(x + i) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        v[j] = (wp && i < n) ? *reinterpret_cast<const float4*>(y + i) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    }
+    if (wp) {
+        float sum = 0.0f;
+#pragma unroll
+        for (int j = 0; j < SW_VEC; j++) sum += (v[j].x + v[j].y) + (v[j].z + v[j].w);
+        const float mean = block_sum(sum, scratch) / (float)n;
+        float ss = 0.0f;
+#pragma unroll
+        for (int j = 0; j < SW_VEC; j++)
+            if ((tid + j * SW_THREADS) * 4 < n) {
+                const float d0 = v[j].x - mean, d1 = v[j].y - mean, d2 = v[j].z - mean, d3 = v[j].w - mean;
+                ss = fmaf(d0, d0, ss); ss = fmaf(d1, d1, ss); ss = fmaf(d2, d2, ss); ss = fmaf(d3, d3, ss);
+            }
+        const float inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)n + eps);
+#pragma unroll
+        for (int j = 0; j < SW_VEC; j++) {
+            const int i = (tid + j * SW_THREADS) * 4;
+            if (i < n) {
+                const float4 w4 = *reinterpret_cast<const float4*>(wp + i), b4 = *reinterpret_cast<const float4*>(bp + i);
+                u[j].x += fmaf((v[j].x - mean) * inv, w4.x, b4.x);
+                u[j].y += fmaf((v[j].y - mean) * inv, w4.y, b4.y);
+                u[j].z += fmaf((v[j].z - mean) * inv, w4.z, b4.z);
+                u[j].w += fmaf((v[j].w - mean) * inv, w4.w, b4.w);
+                *reinterpret_cast<float4*>(x + i) = u[j];
+            }
+        }
+    }
+    if (y) {
+#pragma unroll
+        for (int j = 0; j < SW_VEC; j++) {
+            const int i = (tid + j * SW_THREADS) * 4;
+            if (i < n) *reinterpret_cast<float4*>(y + i) = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        }
+    }
+    if (!wn) return;
+    float sum = 0.0f;
+#pragma unroll
+    for (int j = 0; j < SW_VEC; j++) sum += (u[j].x + u[j].y) + (u[j].z + u[j].w);
+    const float mean = block_sum(sum, scratch) / (float)n;
+    float ss = 0.0f;
+#pragma unroll
+    for (int j = 0; j < SW_VEC; j++)
+        if ((tid + j * SW_THREADS) * 4 < n) {
+            const float d0 = u[j].x - mean, d1 = u[j].y - mean, d2 = u[j].z - mean, d3 = u[j].w - mean;
+            ss = fmaf(d0, d0, ss); ss = fmaf(d1, d1, ss); ss = fmaf(d2, d2, ss); ss = fmaf(d3, d3, ss);
+        }
+    const float inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)n + eps);
+#pragma unroll
+    for (int j = 0; j < SW_VEC; j++) {
+        const int i = (tid + j * SW_THREADS) * 4;
+        if (i < n) {
+            const float4 w4 = *reinterpret_cast<const float4*>(wn + i), b4 = *reinterpret_cast<const float4*>(bn + i);
+            sw_store4<T>(xn + i, fmaf((u[j].x - mean) * inv, w4.x, b4.x), fmaf((u[j].y - mean) * inv, w4.y, b4.y),
+                         fmaf((u[j].z - mean) * inv, w4.z, b4.z), fmaf((u[j].w - mean) * inv, w4.w, b4.w));
+        }
+    }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(SW_THREADS) sandwich_step_kernel(float* __restrict__ x, float* __restrict__ y, const float* __restrict__ wp,
                                                                    const float* __restrict__ bp, const float* __restrict__ wn,
-                                                                   const float* __restrict__ bn, T* __restrict__ xn, int n, float eps) {
+                                                                   const float* __restrict__ bn, T* __restrict__ xn, int n, float eps, int vec) {
     __shared__ float scratch[32];
     dependency_wait();
     let_dependents_start();
     const size_t base = (size_t)blockIdx.x * n;
     const int tid = threadIdx.x;
+    if (vec) {
+        sandwich_row_vec<T>(x + base, y ? y + base : nullptr, wp, bp, wn, bn, xn ? xn + base : nullptr, n, eps, scratch);
+        return;
+    }
     float v[SW_KEEP];
     if (wp) {
         float sum = 0.0f;
@@ -216,8 +307,12 @@ VK_API int vk_sandwich_step(float* x, float* y, const float* w_post, const float
                             int n, float eps, int dtype, cudaStream_t stream) {
     if (rows <= 0) return VK_OK;
     if (n <= 0 || (w_post && (!y || !b_post)) || (w_next && (!b_next || !xn))) return VK_BAD_SHAPE;
+    auto on16 = [](const void* p) { return ((uintptr_t)p % 16) == 0; };
+    const int vec = (n % 4 == 0 && n <= 4 * SW_THREADS * SW_VEC && on16(x) && on16(y) && on16(w_post) && on16(b_post) && on16(w_next) && on16(b_next) &&
+                     ((uintptr_t)xn % (dtype == 0 ? 16 : 8)) == 0) ? 1 : 0;
     if (dtype == 0)
-        return launch_dependent(sandwich_step_kernel<float>, dim3(rows), dim3(SW_THREADS), 0, stream, x, y, w_post, b_post, w_next, b_next, (float*)xn, n, eps);
+        return launch_dependent(sandwich_step_kernel<float>, dim3(rows), dim3(SW_THREADS), 0, stream, x, y, w_post, b_post, w_next, b_next, (float*)xn, n, eps,
+                                vec);
     return launch_dependent(sandwich_step_kernel<__nv_bfloat16>, dim3(rows), dim3(SW_THREADS), 0, stream, x, y, w_post, b_post, w_next, b_next,
-                            (__nv_bfloat16*)xn, n, eps);
+                            (__nv_bfloat16*)xn, n, eps, vec);
 }
