@@ -796,9 +796,9 @@ TINEVIK_SIZES = {
 
 def tinevik_config(sz):
     H, G, dk, dv = sz["heads"], sz["kv"], sz["dim"], sz["vdim"]
-    att = dict(heads=2 * H, kv_heads=G, dim=dk, vdim=dv, scale=dk ** -0.5, softcap=50.0, rot=dict(base=500000.0, dims=dk // 2, scaling=dict(factor=2.0)))
+    att = dict(heads=2 * H, kv_heads=G, dim=dk, vdim=dv, scale=dk ** -0.5, softcap=30.0, rot=dict(base=100000.0, dims=dk // 2, scaling=dict(factor=4.0)))
     lat = dict(heads=2 * H, dim=dk, vdim=dv, kv_rank=sz["kv_rank"], q_rank=sz["q_rank"], scale=dk ** -0.5, mask=dict(size=sz["window"]))
-    mem = dict(heads=H, dim=dk, vdim=2 * dv, tau=16.0)
+    mem = dict(heads=H, dim=dk, vdim=2 * dv, tau=8.0)
     moe = dict(kind="moe", expert=dict(ff=sz["ff"] // 2, limit=7.0), router=dict(experts=MANATAR_EXPERTS, top=MANATAR_TOP))
     kinds = {3: ("attention", att), 7: ("latent_attention", lat)}
     layers = [dict(type=kinds.get(i % 8, ("gla", mem))[0], mixer=kinds.get(i % 8, ("gla", mem))[1],

@@ -78,10 +78,10 @@ CFG_ODD = config(61, 40, [layer("gla", gla(3, 10, 7, 1.0), moe(12, 2.0, 7, 3), w
                           layer("gla", gla(3, 10, 7, 1.0), moe(12, 2.0, 7, 3)),
                           layer("latent_attention", lat(5, 6, 10, 12, 20, 0.5), moe(20, 1.0, 2, 2))], eps=1e-6)
 # wider heads, tensor-core sizes, a window of several pages, the whole head turned
-CFG_WIDE = config(83, 128, [layer("attention", att(4, 1, 64, 64, 0.125, 30.0, rot(500000.0, 64, 8.0)), moe(64, 1.5, 8, 2)),
-                            layer("gla", gla(2, 64, 128, 16.0), dense(256)),
+CFG_WIDE = config(83, 128, [layer("attention", att(4, 1, 64, 64, 0.125, 30.0, rot(200000.0, 64, 8.0)), moe(64, 1.25, 8, 2)),
+                            layer("gla", gla(2, 64, 128, 12.0), dense(256)),
                             layer("latent_attention", lat(4, 32, 64, 64, 96, 0.18, 50), dense(128)),
-                            layer("gla", gla(4, 32, 32, 8.0), moe(64, 1.5, 8, 2))],
+                            layer("gla", gla(4, 32, 32, 8.0), moe(64, 1.25, 8, 2))],
                   embed_scale=11.3, logit_scale=2.0)
 
 CONFIGS = {"all": CFG_ALL, "odd": CFG_ODD, "wide": CFG_WIDE}

@@ -83,9 +83,9 @@ class SandwichNormBlock(Block):
     """x <- x + post(sublayer(pre(x))) for the mixer and then (unless absent) the feed-forward; the four norms are layer norms with
     weight and bias (anything with .weight, .bias and .eps of the LayerNorm part).
 
-    The sublayers keep the framework's contract (they ADD their result into a float32 buffer): the buffer is a zeroed row y, and ONE
-    kernel between two sublayers norms y, sums it into the float32 residual row, zeroes y again and norms the new row for the next
-    sublayer.  A block leaves its last sum pending for the next block's first kernel (two launches a layer instead of three); behind
+    The sublayers do what they do everywhere in the framework (they ADD their result into a float32 buffer): the buffer is a zeroed row
+    y, and ONE kernel between two sublayers norms y, sums it into the float32 residual row, zeroes y again and norms the new row for the
+    next sublayer.  A block leaves its last sum pending for the next block's first kernel (two launches a layer instead of three); behind
     the last block SandwichFlush, the decoder's `collect` part, does what is left.  While something looks at the residual rows
     between the runs of the schedule (ctx.after_run), every block finishes its own sum."""
 
